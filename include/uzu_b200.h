@@ -450,6 +450,111 @@ UZU_API void uzu_delta_net_fused_update_encode(uzu_command_buffer* cmd, const uz
  * instead of one decode-kernel launch per token. NOT yet run on hardware (round 1). */
 UZU_API void uzu_debug_set_delta_prefill(int mode);
 
+/* ---- Kernels of the parallel-block family (Punilix): 32-bit residual stream, dense (unquantised) weights ------------------- *
+ * Extensions (the reference has no such model). Activations between kernels are f32; weights and the latent KV cache carry the
+ * engine's storage type (`UZU_DT_BF16` or `UZU_DT_F32`); sums, norms, scores, decays and recurrent state are f32 always. */
+
+/* D[z][p, :] (+)= scale * A[z][row(p), :] . W[z]^T for every compact row p. W is [n, k] row-major (out, in).
+ *   z-batching: operand z starts at a + z*a_z_stride (f32 elements), w + z*w_z_stride (weight elements), d + z*d_z_stride (f32 elements).
+ *   row groups (group_offsets != 0): z is a group index, compact rows [group_offsets[z], group_offsets[z+1]) use weight z; rows_map
+ *   (optional u32 [rows]) names the A row a compact row reads (identity when 0). D rows are always compact. m is then an upper
+ *   bound of the rows of one group. All f32 accumulation; with bf16 weights and m >= 32 the products run on the tensor pipe with A
+ *   rounded to bf16, otherwise as f32 multiply-adds. */
+typedef struct uzu_dense_linear_args {
+    uint64_t a;                    /* f32 [m, lda] */
+    uint64_t w;                    /* weights_dt [n, k] per z */
+    uint64_t d;                    /* f32 [m, ldd] */
+    uint64_t bias;                 /* optional f32 [n] (z = 0 only) */
+    uint64_t group_offsets;        /* optional u32 [batch + 1] (device) */
+    uint64_t rows_map;             /* optional u32 [rows] (device) */
+    uint64_t a_z_stride, w_z_stride, d_z_stride;
+    uint32_t m, n, k, lda, ldd, batch;   /* batch = number of z (>= 1) */
+    uint32_t weights_dt, accumulate;
+    float scale;                   /* applied to the product before bias / accumulation */
+    uint32_t reserved;
+} uzu_dense_linear_args;
+UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
+
+/* RMS norm in `groups` equal consecutive parts of a row: part / sqrt(mean(part^2) + epsilon), whole row times scales.
+ * input f32 [rows, in_stride] (first n columns), optional row gather, output f32 [rows, out_stride]. groups = 1 is the plain RMS norm. */
+typedef struct uzu_group_rms_norm_args {
+    uint64_t input, scales /* f32 [n], 0 = none */, output, row_indices /* optional u32 [rows] */;
+    uint32_t rows, n, groups, in_stride, out_stride;
+    float epsilon;
+} uzu_group_rms_norm_args;
+UZU_API void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_rms_norm_args* args);
+
+/* Elementwise glue, all f32.
+ *   embedding_f32:   out[r, :] = table[token[r], :] (table weights_dt [vocab, n])
+ *   clamped_glu:     g = min(gate, limit); u = clamp(up, -limit, limit); out = g * sigmoid(alpha * g) * (u + 1); gate / up are column
+ *                    ranges [0, f) and [f, 2f) of a [rows, 2f] operand
+ *   unary_f32:       out = op(in) over a strided column range; op 0 = tanh
+ *   residual_add:    x += a (+ b when b != 0)
+ *   logit_cap_f32:   l = cap * tanh(l / cap) (has_cap), and a bf16 copy for the sampling kernels */
+UZU_API void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output,
+                                      uint32_t rows, uint32_t vocab, uint32_t n);
+UZU_API void uzu_clamped_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f, float limit, float alpha);
+UZU_API void uzu_unary_f32_encode(uzu_command_buffer* cmd, uint64_t input, uint32_t in_stride, uint64_t output, uint32_t out_stride,
+                                  uint32_t rows, uint32_t n, uint32_t op);
+UZU_API void uzu_residual_add_encode(uzu_command_buffer* cmd, uint64_t x, uint64_t a, uint64_t b, uint32_t length);
+UZU_API void uzu_logit_cap_f32_encode(uzu_command_buffer* cmd, uint64_t logits_f32, uint64_t logits_bf16, uint32_t length, float cap, uint32_t has_cap);
+
+/* Table-routed experts: a [vocab, top] i32 table names the experts of a token id. route builds, for the `rows` tokens of a pass, the
+ * expert-sorted pair list: group_offsets u32 [experts + 1], rows_map u32 [rows*top] (token row of a compact pair), pair_pos u32
+ * [rows*top] (compact position of pair (row, slot)). combine: out[r, :] (+)= weight * sum_slot pairs[pair_pos[r*top + slot], :]. */
+typedef struct uzu_table_route_args {
+    uint64_t token_ids, table, group_offsets, rows_map, pair_pos;
+    uint32_t rows, top, experts, vocab;
+} uzu_table_route_args;
+UZU_API void uzu_table_route_encode(uzu_command_buffer* cmd, const uzu_table_route_args* args);
+UZU_API void uzu_routed_combine_encode(uzu_command_buffer* cmd, uint64_t pairs, uint64_t pair_pos, uint64_t output, uint32_t rows, uint32_t top,
+                                       uint32_t n, float weight, uint32_t accumulate);
+
+/* Generalized delta rule, `rows` tokens of one sequence in token order in one launch, state f32 [heads, dim, dim] (key channel major)
+ * carried in `state`:  d = exp(-e^-1/2 * sigmoid(decay_logit + decay_bias)); a = sigmoid(rate_logit + rate_bias);
+ * u = k / sqrt(sum k^2 + 1e-6); S <- diag(d) S - (a*u)(u^T S) + k v^T (both terms read the old S); out = S^T r.
+ * r, k, v, rate_logit, decay_logit: f32 with row strides (elements) and [heads*dim] columns. */
+typedef struct uzu_general_delta_args {
+    uint64_t r, k, v, rate_logit, decay_logit;
+    uint64_t rate_bias, decay_bias;          /* f32 [heads*dim] */
+    uint64_t state, out;                     /* out f32 [rows, heads*dim] */
+    uint32_t r_stride, k_stride, v_stride, rate_stride, decay_stride;
+    uint32_t rows, heads, dim;
+} uzu_general_delta_args;
+UZU_API void uzu_general_delta_encode(uzu_command_buffer* cmd, const uzu_general_delta_args* args);
+
+/* out[r, h, :] = x[r, h, :] / sqrt(mean(x[r, h, :]^2) + epsilon) * scales[h*dim + :] * sigmoid(gate[r, h*dim + :]); scales / gate optional */
+typedef struct uzu_head_norm_gate_args {
+    uint64_t x, scales, gate, out;
+    uint32_t rows, heads, dim, x_stride, gate_stride, out_stride, normalize;
+    float epsilon;
+} uzu_head_norm_gate_args;
+UZU_API void uzu_head_norm_gate_encode(uzu_command_buffer* cmd, const uzu_head_norm_gate_args* args);
+
+/* Latent attention, cache side and query side of one pass. Per token row t (absolute position p = prefix + t, prefix read from
+ * dynamic_position when non-zero):
+ *   cache row p = [ rms(kv[t, 0:rank]) * latent_scales | rotate(kv[t, rank:rank+rot_dim]) ]  (cache_dt)
+ *   query[t, h, rank:rank+rot_dim] = rotate(q[t, h, dim:dim+rot_dim])   (query f32 [rows, heads, rank + rot_dim]; the first `rank`
+ *   columns of every head are filled by the absorbed-key projection, a z-batched dense linear)
+ * rotate: interleaved pairs (2i, 2i+1) of the first rot_pairs*2 entries by cos/sin rows [positions, rot_pairs] f32 (already scaled). */
+typedef struct uzu_latent_prepare_args {
+    uint64_t kv, q, query, cache, latent_scales, cosines, sines, dynamic_position;
+    uint32_t rows, heads, dim, rot_dim, rank, rot_pairs, kv_stride, q_stride, prefix, cache_dt;
+    float epsilon;
+    uint32_t reserved;
+} uzu_latent_prepare_args;
+UZU_API void uzu_latent_prepare_encode(uzu_command_buffer* cmd, const uzu_latent_prepare_args* args);
+
+/* Causal softmax attention of `rows` queries over the latent cache shared by all heads: score(t, h, j) = scale * query[t,h,:] .
+ * cache[j,:] for j <= prefix + t, out[t, h, :] = sum_j softmax_j * cache[j, 0:rank]  (f32 [rows, heads, rank]). */
+typedef struct uzu_latent_attention_args {
+    uint64_t query, cache, out, dynamic_position;
+    uint32_t rows, heads, rank, rot_dim, prefix, cache_dt;
+    float scale;
+    uint32_t reserved;
+} uzu_latent_attention_args;
+UZU_API void uzu_latent_attention_encode(uzu_command_buffer* cmd, const uzu_latent_attention_args* args);
+
 /* ---- Host engine (C++ mirror of the reference's backend-agnostic Rust host code) ---------- *
  * No Rust toolchain exists in the build image, so the layer above the kernels -- Engine /
  * LanguageModel / LanguageModelStream / Decoder / Transformer / TransformerLayer (engine/mod.rs:15-43,
@@ -462,7 +567,9 @@ typedef struct uzu_engine_options {
     uint32_t use_cuda_graph;       /* capture the per-token command list once and replay it */
     uint32_t fused_decode;         /* use the fused decode kernels (norm->GEMV prologue, act->GEMV prologue, ...) */
     uint32_t tp_rank, tp_size;     /* tensor-parallel shard of this process (1 = none) */
-    uint64_t reserved[4];
+    uint32_t storage_f32;          /* models with dense weights: keep weights, cache and every product in true f32 (parity runs) */
+    uint32_t reserved0;
+    uint64_t reserved[3];
 } uzu_engine_options;
 typedef enum uzu_sampling_kind { UZU_SAMPLING_GREEDY = 0, UZU_SAMPLING_STOCHASTIC = 1 } uzu_sampling_kind;
 typedef struct uzu_sampling_method {      /* encodable_block/sampling/mod.rs:44-56 */
@@ -507,6 +614,17 @@ UZU_API uzu_status uzu_engine_decode_device(uzu_engine* e, uint32_t steps, uint6
  * state, copy bf16 logits of rows [row_begin,row_end) to `out_logits` (HOST, u16 bits) and synchronize. */
 UZU_API uzu_status uzu_engine_forward(uzu_engine* e, const uint32_t* tokens, uint32_t count, uint32_t row_begin,
                                       uint32_t row_end, uint16_t* out_logits);
+/* Sequence slots (extension): independent sequence states (caches, recurrent states, positions) beside the engine's own, acquired and
+ * released one by one; a released slot's pages and states are reused by the next acquire (reset on acquire).
+ * forward_rows: feed the next `count` tokens (HOST) of a slot (UZU_MAIN_SLOT = the engine's own state) in passes of <= 1024 tokens and
+ * copy the f32 logits of the listed rows (ascending indices into `tokens`) to out_logits (HOST, [nrows, vocab]). Nothing is sampled. */
+#define UZU_MAIN_SLOT 0xFFFFFFFFu
+UZU_API uzu_status uzu_engine_slot_acquire(uzu_engine* e, uint32_t* out_slot);
+UZU_API uzu_status uzu_engine_slot_release(uzu_engine* e, uint32_t slot);
+UZU_API uzu_status uzu_engine_forward_rows(uzu_engine* e, uint32_t slot, const uint32_t* tokens, uint32_t count, const uint32_t* rows,
+                                           uint32_t nrows, float* out_logits);
+/* f32 residual stream after every layer of the last pass (models of the parallel-block family; debug / parity): [layers, count, model_dim] */
+UZU_API uzu_status uzu_engine_debug_layer_outputs(uzu_engine* e, uint32_t enable, float* out, uint32_t capacity_floats, uint32_t* out_count);
 /* Multi-sequence batched decode (extension -- the reference decodes ONE sequence; BASELINE config 4 "batch = 8"): `sequences` (<= 16)
  * independent sequence states (own KV caches / DeltaNet states / positions) advance by one token per step and share one pass over the
  * weights (every linear runs with m = sequences rows); attention and the DeltaNet recurrence run per sequence. Greedy sampling.

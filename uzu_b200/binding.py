@@ -112,7 +112,7 @@ DeltaNetFusedUpdateArgs = _struct("uzu_delta_net_fused_update_args", [("update",
 
 EngineOptions = _struct("uzu_engine_options", [
     ("max_context_length", u32), ("use_cuda_graph", u32), ("fused_decode", u32), ("tp_rank", u32), ("tp_size", u32),
-    ("reserved", u64 * 4)])
+    ("storage_f32", u32), ("reserved0", u32), ("reserved", u64 * 3)])
 
 SamplingMethod = _struct("uzu_sampling_method", [
     ("kind", u32), ("has_temperature", u32), ("temperature", f32), ("has_top_k", u32), ("top_k", u32), ("has_top_p", u32),
@@ -130,7 +130,46 @@ FusedLinearArgs = _struct("uzu_fused_linear_args", [
     ("norm_epsilon", f32), ("norm_scale_offset", f32), ("norm_residual_add", u32), ("norm_full_layer", u32), ("act_operand", u64),
     ("act_type", u32), ("sg_attn", u64), ("sg_gate", u64), ("epilogue", u32), ("reserved0", u32), ("decode_stream", u64)])
 
-ABI_STRUCTS = [DeltaNetFusedUpdateArgs, QkNormConfig, AttentionPrepareNormArgs, FusedLinearArgs, RingParams, TrieNode, KvCopy, MatmulArgs, NormalizationArgs, QkvNormArgs, AttentionPrepareArgs, AttentionArgs,
+# kernels of the parallel-block family (f32 activations, dense bf16 / f32 weights)
+DenseLinearArgs = _struct("uzu_dense_linear_args", [
+    ("a", u64), ("w", u64), ("d", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64),
+    ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64),
+    ("m", u32), ("n", u32), ("k", u32), ("lda", u32), ("ldd", u32), ("batch", u32),
+    ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("reserved", u32)])
+
+GroupRmsNormArgs = _struct("uzu_group_rms_norm_args", [
+    ("input", u64), ("scales", u64), ("output", u64), ("row_indices", u64),
+    ("rows", u32), ("n", u32), ("groups", u32), ("in_stride", u32), ("out_stride", u32), ("epsilon", f32)])
+
+TableRouteArgs = _struct("uzu_table_route_args", [
+    ("token_ids", u64), ("table", u64), ("group_offsets", u64), ("rows_map", u64), ("pair_pos", u64),
+    ("rows", u32), ("top", u32), ("experts", u32), ("vocab", u32)])
+
+GeneralDeltaArgs = _struct("uzu_general_delta_args", [
+    ("r", u64), ("k", u64), ("v", u64), ("rate_logit", u64), ("decay_logit", u64), ("rate_bias", u64), ("decay_bias", u64),
+    ("state", u64), ("out", u64),
+    ("r_stride", u32), ("k_stride", u32), ("v_stride", u32), ("rate_stride", u32), ("decay_stride", u32),
+    ("rows", u32), ("heads", u32), ("dim", u32)])
+
+HeadNormGateArgs = _struct("uzu_head_norm_gate_args", [
+    ("x", u64), ("scales", u64), ("gate", u64), ("out", u64),
+    ("rows", u32), ("heads", u32), ("dim", u32), ("x_stride", u32), ("gate_stride", u32), ("out_stride", u32), ("normalize", u32),
+    ("epsilon", f32)])
+
+LatentPrepareArgs = _struct("uzu_latent_prepare_args", [
+    ("kv", u64), ("q", u64), ("query", u64), ("cache", u64), ("latent_scales", u64), ("cosines", u64), ("sines", u64),
+    ("dynamic_position", u64),
+    ("rows", u32), ("heads", u32), ("dim", u32), ("rot_dim", u32), ("rank", u32), ("rot_pairs", u32), ("kv_stride", u32),
+    ("q_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("reserved", u32)])
+
+LatentAttentionArgs = _struct("uzu_latent_attention_args", [
+    ("query", u64), ("cache", u64), ("out", u64), ("dynamic_position", u64),
+    ("rows", u32), ("heads", u32), ("rank", u32), ("rot_dim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32), ("reserved", u32)])
+
+MAIN_SLOT = 0xFFFFFFFF
+
+ABI_STRUCTS = [DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
+               DeltaNetFusedUpdateArgs, QkNormConfig, AttentionPrepareNormArgs, FusedLinearArgs, RingParams, TrieNode, KvCopy, MatmulArgs, NormalizationArgs, QkvNormArgs, AttentionPrepareArgs, AttentionArgs,
                AttentionTwoPass2Args, KvCacheUpdateArgs, GatedActMulArgs, QuantizedEmbeddingLookupArgs, UnifiedSamplingArgs,
                DeltaNetConvUpdateArgs, DeltaNetUpdateArgs, EngineOptions, SamplingMethod, ModelInfo, TpAllGatherArgs]
 
@@ -157,7 +196,10 @@ uzu_delta_net_fused_update_supported uzu_delta_net_fused_update_encode uzu_engin
 uzu_context_tp_rank uzu_tp_p2p_export uzu_tp_p2p_import uzu_tp_all_reduce_encode uzu_tp_all_gather_encode uzu_fused_linear_supported uzu_fused_linear_encode
 uzu_engine_decode_mode uzu_engine_decode_mode_reason uzu_engine_set_decode_mode uzu_engine_last_logits uzu_engine_debug_decode_trace
 uzu_engine_speculation_supported uzu_engine_trie_pass uzu_engine_trie_accept uzu_activation_transform_encode
-uzu_activation_transform_validate""".split()
+uzu_activation_transform_validate uzu_dense_linear_encode uzu_group_rms_norm_encode uzu_embedding_f32_encode uzu_clamped_glu_encode
+uzu_unary_f32_encode uzu_residual_add_encode uzu_logit_cap_f32_encode uzu_table_route_encode uzu_routed_combine_encode
+uzu_general_delta_encode uzu_head_norm_gate_encode uzu_latent_prepare_encode uzu_latent_attention_encode
+uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs""".split()
 
 _lib = None
 
@@ -289,6 +331,23 @@ def load() -> C.CDLL:
         "uzu_tp_all_gather_encode": (None, [vp, C.POINTER(TpAllGatherArgs)]),
         "uzu_fused_linear_supported": (C.c_int, [vp, C.POINTER(FusedLinearArgs)]),
         "uzu_fused_linear_encode": (None, [vp, C.POINTER(FusedLinearArgs)]),
+        "uzu_dense_linear_encode": (None, [vp, C.POINTER(DenseLinearArgs)]),
+        "uzu_group_rms_norm_encode": (None, [vp, C.POINTER(GroupRmsNormArgs)]),
+        "uzu_embedding_f32_encode": (None, [vp, u64, u64, u32, u64, u32, u32, u32]),
+        "uzu_clamped_glu_encode": (None, [vp, u64, u64, u32, u32, f32, f32]),
+        "uzu_unary_f32_encode": (None, [vp, u64, u32, u64, u32, u32, u32, u32]),
+        "uzu_residual_add_encode": (None, [vp, u64, u64, u64, u32]),
+        "uzu_logit_cap_f32_encode": (None, [vp, u64, u64, u32, f32, u32]),
+        "uzu_table_route_encode": (None, [vp, C.POINTER(TableRouteArgs)]),
+        "uzu_routed_combine_encode": (None, [vp, u64, u64, u64, u32, u32, u32, f32, u32]),
+        "uzu_general_delta_encode": (None, [vp, C.POINTER(GeneralDeltaArgs)]),
+        "uzu_head_norm_gate_encode": (None, [vp, C.POINTER(HeadNormGateArgs)]),
+        "uzu_latent_prepare_encode": (None, [vp, C.POINTER(LatentPrepareArgs)]),
+        "uzu_latent_attention_encode": (None, [vp, C.POINTER(LatentAttentionArgs)]),
+        "uzu_engine_slot_acquire": (C.c_int, [vp, C.POINTER(u32)]),
+        "uzu_engine_slot_release": (C.c_int, [vp, u32]),
+        "uzu_engine_forward_rows": (C.c_int, [vp, u32, C.POINTER(u32), u32, C.POINTER(u32), u32, C.POINTER(C.c_float)]),
+        "uzu_engine_debug_layer_outputs": (C.c_int, [vp, u32, C.POINTER(C.c_float), u32, C.POINTER(u32)]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -443,10 +502,11 @@ class CommandBuffer:
 class Engine:
     """Engine + LanguageModel + LanguageModelState + stream (engine/language_model/*)."""
 
-    def __init__(self, ctx: Context, model_dir, max_context_length=8192, use_cuda_graph=True, fused_decode=True, tp_rank=0, tp_size=1):
+    def __init__(self, ctx: Context, model_dir, max_context_length=8192, use_cuda_graph=True, fused_decode=True, tp_rank=0, tp_size=1,
+                 storage_f32=False):
         self.ctx, self.lib = ctx, ctx.lib
         opts = EngineOptions(max_context_length=max_context_length, use_cuda_graph=int(use_cuda_graph),
-                             fused_decode=int(fused_decode), tp_rank=tp_rank, tp_size=tp_size)
+                             fused_decode=int(fused_decode), tp_rank=tp_rank, tp_size=tp_size, storage_f32=int(storage_f32))
         h = C.c_void_p()
         _check(self.lib.uzu_engine_create(ctx.h, str(model_dir).encode(), C.byref(opts), C.byref(h)))
         self.h = h
@@ -527,6 +587,34 @@ class Engine:
         _check(self.lib.uzu_engine_forward(self.h, tokens.ctypes.data_as(C.POINTER(u32)), n, row_begin, row_end,
                                            out.ctypes.data_as(C.POINTER(C.c_uint16))))
         return out
+
+    # sequence slots: independent sequence states beside the engine's own (acquire / release / feed tokens and read f32 logits)
+    def slot_acquire(self) -> int:
+        out = u32()
+        _check(self.lib.uzu_engine_slot_acquire(self.h, C.byref(out)))
+        return out.value
+
+    def slot_release(self, slot: int):
+        _check(self.lib.uzu_engine_slot_release(self.h, slot))
+
+    def forward_rows(self, tokens, rows=(), slot: int = MAIN_SLOT) -> np.ndarray:
+        """Feed the next tokens of a slot; f32 logits [len(rows), vocab] of the listed (ascending) token indices. Nothing is sampled."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.uint32)
+        rows = np.ascontiguousarray(rows, dtype=np.uint32)
+        out = np.zeros((len(rows), self.info.vocab_size), dtype=np.float32)
+        _check(self.lib.uzu_engine_forward_rows(self.h, slot, tokens.ctypes.data_as(C.POINTER(u32)), len(tokens),
+                                                rows.ctypes.data_as(C.POINTER(u32)), len(rows), out.ctypes.data_as(C.POINTER(C.c_float))))
+        return out
+
+    def debug_layer_outputs(self, enable=True) -> np.ndarray | None:
+        """Switch the per-layer residual dump on / off; with it on, returns [layers, rows, model_dim] f32 of the last pass (None before one)."""
+        n = u32()
+        _check(self.lib.uzu_engine_debug_layer_outputs(self.h, int(enable), None, 0, C.byref(n)))
+        if not enable or n.value == 0:
+            return None
+        out = np.zeros(n.value, dtype=np.float32)
+        _check(self.lib.uzu_engine_debug_layer_outputs(self.h, 1, out.ctypes.data_as(C.POINTER(C.c_float)), n.value, C.byref(n)))
+        return out.reshape(self.info.num_layers, -1, self.info.model_dim)
 
     @property
     def launch_count(self):

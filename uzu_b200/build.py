@@ -37,12 +37,16 @@ SOURCES = {
     "deltanet.cu": ["-fmad=false"],
     "deltanet_prefill.cu": ["-fmad=false"],
     "decode_mega.cu": [],
+    "dense_linear.cu": [],
+    "residual_f32.cu": [],
+    "general_delta.cu": [],
+    "latent_attention.cu": [],
     "engine.cu": [],
 }
 
 
 def _deps_digest() -> bytes:
-    hdrs = sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [HERE.parent / "include" / "uzu_b200.h"])
+    hdrs = sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.inl")) + [HERE.parent / "include" / "uzu_b200.h"])
     h = hashlib.sha1()
     for f in hdrs:
         h.update(f.name.encode())

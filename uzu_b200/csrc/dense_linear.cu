@@ -1,0 +1,331 @@
+// Dense (unquantised) linear: D (+)= scale * A . W^T, f32 activations, bf16 or f32 weights [n, k], f32 accumulation.
+// Three kernels behind one entry point (uzu_dense_linear_encode):
+//   rows kernel   (<= 8 rows per group): one warp per output feature, the weight row streamed once with 128-bit loads and multiplied
+//                 with every activation row in f32 -- the decode step's weight pass, bound by the weight bytes;
+//   tensor kernel (bf16 weights, >= 32 rows): 64 x 64 output tiles on mma.sync.m16n8k16 (bf16 x bf16 -> f32), A rounded to bf16 while
+//                 it is staged, double-buffered shared-memory tiles;
+//   tile kernel   (everything else, and every f32-weight product of more than 8 rows): 64 x 64 tiles of f32 multiply-adds.
+// All three share the operand addressing: z-batches (per-head weights: operand z starts z*stride further in A, W and D) and row groups
+// (per-expert weights: compact rows [off[z], off[z+1]) use weight z, an optional map names the activation row a compact row reads).
+#include <mma.h>
+
+#include "common.cuh"
+
+namespace uzu {
+
+struct DenseRows {
+    uint32_t begin, count;
+};
+
+__device__ __forceinline__ DenseRows dense_rows(const uzu_dense_linear_args& a, uint32_t z) {
+    if (a.group_offsets) {
+        const uint32_t* off = reinterpret_cast<const uint32_t*>(a.group_offsets);
+        const uint32_t b = off[z], e = off[z + 1];
+        return {b, e - b};
+    }
+    return {0u, a.m};
+}
+
+template <typename TW>
+__device__ __forceinline__ float w_to_f32(TW v);
+template <>
+__device__ __forceinline__ float w_to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float w_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, float* d, uint32_t z, uint32_t col, float acc) {
+    float v = acc * a.scale;
+    if (a.bias && z == 0) v += reinterpret_cast<const float*>(a.bias)[col];
+    if (a.accumulate) v += *d;
+    *d = v;
+}
+
+// ---- rows kernel ------------------------------------------------------------------------------------------------------------------
+constexpr int DL_MAX_ROWS = 8;
+
+template <typename TW>
+__global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_args a) {
+    const uint32_t z = blockIdx.y;
+    const int lane = threadIdx.x & 31;
+    const uint32_t col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_launch_dependents();
+    if (col >= a.n) return;
+    const TW* w = reinterpret_cast<const TW*>(a.w) + (size_t)z * a.w_z_stride + (size_t)col * a.k;
+    constexpr int VEC = 16 / (int)sizeof(TW);            // weights per 128-bit load
+    const bool vec_ok = (a.k % VEC == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (a.lda % 4 == 0) && ((a.a & 15) == 0) &&
+                        (a.a_z_stride % 4 == 0);
+    // the weight row does not depend on the previous kernel: with programmatic dependent launch its first loads overlap that kernel's tail
+    uint4 first = make_uint4(0, 0, 0, 0);
+    const bool have_first = vec_ok && (uint32_t)lane * VEC < a.k;
+    if (have_first) first = ldg_stream_u4(w + (size_t)lane * VEC);
+    pdl_wait();
+    const DenseRows R = dense_rows(a, z);
+    if (R.count == 0) return;
+    const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
+    const float* arow[DL_MAX_ROWS];
+#pragma unroll
+    for (int r = 0; r < DL_MAX_ROWS; ++r) {
+        const uint32_t p = R.begin + ((uint32_t)r < R.count ? r : 0);
+        arow[r] = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride + (size_t)(map ? map[p] : p) * a.lda;
+    }
+    float acc[DL_MAX_ROWS];
+#pragma unroll
+    for (int r = 0; r < DL_MAX_ROWS; ++r) acc[r] = 0.0f;
+    if (vec_ok) {
+        for (uint32_t k0 = lane * VEC; k0 < a.k; k0 += 32 * VEC) {
+            const uint4 raw = (k0 == (uint32_t)lane * VEC) ? first : ldg_stream_u4(w + k0);
+            float wf[VEC];
+            if constexpr (sizeof(TW) == 2) {
+                const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    wf[2 * i] = __uint_as_float(u[i] << 16);
+                    wf[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+                }
+            } else {
+                wf[0] = __uint_as_float(raw.x); wf[1] = __uint_as_float(raw.y); wf[2] = __uint_as_float(raw.z); wf[3] = __uint_as_float(raw.w);
+            }
+#pragma unroll
+            for (int r = 0; r < DL_MAX_ROWS; ++r) {
+                if ((uint32_t)r < R.count) {
+#pragma unroll
+                    for (int i = 0; i < VEC; i += 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
+                        acc[r] = fmaf(x.x, wf[i], acc[r]);
+                        acc[r] = fmaf(x.y, wf[i + 1], acc[r]);
+                        acc[r] = fmaf(x.z, wf[i + 2], acc[r]);
+                        acc[r] = fmaf(x.w, wf[i + 3], acc[r]);
+                    }
+                }
+            }
+        }
+    } else {
+        for (uint32_t k0 = lane; k0 < a.k; k0 += 32) {
+            const float wv = w_to_f32<TW>(w[k0]);
+#pragma unroll
+            for (int r = 0; r < DL_MAX_ROWS; ++r)
+                if ((uint32_t)r < R.count) acc[r] = fmaf(arow[r][k0], wv, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < DL_MAX_ROWS; ++r) {
+        if ((uint32_t)r < R.count) {          // uniform over the warp
+            const float s = warp_sum(acc[r]);
+            if (lane == 0) {
+                float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col;
+                dense_store(a, d, z, col, s);
+            }
+        }
+    }
+}
+
+// ---- tile kernel (f32 multiply-adds) ------------------------------------------------------------------------------------------------
+constexpr int DT_BM = 64, DT_BN = 64, DT_BK = 16;
+
+template <typename TW>
+__global__ void __launch_bounds__(256) dense_tile_kernel(const uzu_dense_linear_args a) {
+    __shared__ float As[DT_BK][DT_BM + 4];
+    __shared__ float Ws[DT_BK][DT_BN + 4];
+    const uint32_t z = blockIdx.z;
+    const DenseRows R = dense_rows(a, z);
+    const uint32_t m0 = blockIdx.y * DT_BM, n0 = blockIdx.x * DT_BN;
+    if (m0 >= R.count) return;
+    const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
+    const float* A = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride;
+    const TW* W = reinterpret_cast<const TW*>(a.w) + (size_t)z * a.w_z_stride;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    // staging: thread loads 4 consecutive k of one row (A) and one feature (W)
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    const uint32_t pa = m0 + lr;
+    const bool a_ok = pa < R.count;
+    const float* a_src = A + (size_t)(a_ok ? (map ? map[R.begin + pa] : R.begin + pa) : 0) * a.lda;
+    const bool w_ok = n0 + lr < a.n;
+    const TW* w_src = W + (size_t)(w_ok ? n0 + lr : 0) * a.k;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (uint32_t k0 = 0; k0 < a.k; k0 += DT_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t k = k0 + lk + i;
+            As[lk + i][lr] = (a_ok && k < a.k) ? a_src[k] : 0.0f;
+            Ws[lk + i][lr] = (w_ok && k < a.k) ? w_to_f32<TW>(w_src[k]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < DT_BK; ++k) {
+            const float4 av = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+            const float4 wv = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+            const float ar[4] = {av.x, av.y, av.z, av.w}, wr[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], wr[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t p = m0 + ty * 4 + i;
+        if (p >= R.count) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t col = n0 + tx * 4 + j;
+            if (col >= a.n) continue;
+            float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + p) * a.ldd + col;
+            dense_store(a, d, z, col, acc[i][j]);
+        }
+    }
+}
+
+// ---- tensor kernel (bf16 weights, mma.sync m16n8k16) --------------------------------------------------------------------------------
+// 128 threads = 4 warps in a 2 x 2 grid, each warp a 32 x 32 part of the 64 x 64 tile = 2 x 4 MMA tiles. K blocks of 32, staged as bf16
+// in shared memory with a row stride of 40 elements (80 bytes: the 8 rows of a fragment load fall into different banks).
+constexpr int TC_BM = 64, TC_BN = 64, TC_BK = 32, TC_LD = 40;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) dense_tensor_kernel(const uzu_dense_linear_args a) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][TC_BM * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][TC_BN * TC_LD];
+    const uint32_t z = blockIdx.z;
+    const DenseRows R = dense_rows(a, z);
+    const uint32_t m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+    if (m0 >= R.count) return;
+    const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
+    const float* A = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride;
+    const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)z * a.w_z_stride;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+    // staging: a thread owns half a row (16 k) of the A tile and of the W tile
+    const int sr = tid >> 1, sk = (tid & 1) * 16;
+    const uint32_t pa = m0 + sr;
+    const bool a_ok = pa < R.count;
+    const float* a_src = A + (size_t)(a_ok ? (map ? map[R.begin + pa] : R.begin + pa) : 0) * a.lda;
+    const bool w_ok = n0 + sr < a.n;
+    const __nv_bfloat16* w_src = W + (size_t)(w_ok ? n0 + sr : 0) * a.k;
+    const bool a_vec = (a.lda % 4 == 0) && ((a.a & 15) == 0) && (a.a_z_stride % 4 == 0) && (a.k % 4 == 0);
+    const bool w_vec = (a.k % 8 == 0) && ((a.w & 15) == 0) && (a.w_z_stride % 8 == 0);
+    float ra[16];
+    __nv_bfloat16 rw[16];
+    auto fetch = [&](uint32_t k0) {
+        const uint32_t kb = k0 + sk;
+        if (a_ok && a_vec && kb + 16 <= a.k) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = *reinterpret_cast<const float4*>(a_src + kb + 4 * i);
+                ra[4 * i] = v.x; ra[4 * i + 1] = v.y; ra[4 * i + 2] = v.z; ra[4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ra[i] = (a_ok && kb + i < a.k) ? a_src[kb + i] : 0.0f;
+        }
+        if (w_ok && w_vec && kb + 16 <= a.k) {
+            *reinterpret_cast<uint4*>(&rw[0]) = *reinterpret_cast<const uint4*>(w_src + kb);
+            *reinterpret_cast<uint4*>(&rw[8]) = *reinterpret_cast<const uint4*>(w_src + kb + 8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) rw[i] = (w_ok && kb + i < a.k) ? w_src[kb + i] : __float2bfloat16_rn(0.0f);
+        }
+    };
+    auto stash = [&](int buf) {
+        __nv_bfloat16* as = &As[buf][sr * TC_LD + sk];
+        __nv_bfloat16* ws = &Ws[buf][sr * TC_LD + sk];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            *reinterpret_cast<__nv_bfloat162*>(as + i) = __floats2bfloat162_rn(ra[i], ra[i + 1]);
+            *reinterpret_cast<__nv_bfloat162*>(ws + i) = __halves2bfloat162(rw[i], rw[i + 1]);
+        }
+    };
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.0f;
+    const uint32_t nk = (a.k + TC_BK - 1) / TC_BK;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    const int g = lane >> 2, t4 = lane & 3;
+    for (uint32_t kb = 0; kb < nk; ++kb) {
+        const int cur = kb & 1;
+        if (kb + 1 < nk) fetch((kb + 1) * TC_BK);
+#pragma unroll
+        for (int ks = 0; ks < TC_BK; ks += 16) {
+            uint32_t af[2][4], bf[4][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const __nv_bfloat16* base = &As[cur][(wm + i * 16 + g) * TC_LD + ks + t4 * 2];
+                af[i][0] = *reinterpret_cast<const uint32_t*>(base);
+                af[i][1] = *reinterpret_cast<const uint32_t*>(base + 8 * TC_LD);
+                af[i][2] = *reinterpret_cast<const uint32_t*>(base + 8);
+                af[i][3] = *reinterpret_cast<const uint32_t*>(base + 8 * TC_LD + 8);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat16* base = &Ws[cur][(wn + j * 8 + g) * TC_LD + ks + t4 * 2];
+                bf[j][0] = *reinterpret_cast<const uint32_t*>(base);
+                bf[j][1] = *reinterpret_cast<const uint32_t*>(base + 8);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], af[i], bf[j]);
+        }
+        if (kb + 1 < nk) stash(cur ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t p = m0 + wm + i * 16 + g + (q >> 1) * 8;
+                const uint32_t col = n0 + wn + j * 8 + t4 * 2 + (q & 1);
+                if (p < R.count && col < a.n) {
+                    float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + p) * a.ldd + col;
+                    dense_store(a, d, z, col, acc[i][j][q]);
+                }
+            }
+}
+
+}  // namespace uzu
+
+extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args) {
+    using namespace uzu;
+    if (!encodable(cmd, "dense_linear")) return;
+    uzu_dense_linear_args a = *args;
+    if (!a.a || !a.w || !a.d || (a.weights_dt != UZU_DT_BF16 && a.weights_dt != UZU_DT_F32) || a.batch == 0 || (a.rows_map && !a.group_offsets && a.batch != 1)) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: null operand / bad dtype / bad batch");
+        return;
+    }
+    if (a.m == 0 || a.n == 0) return;
+    if (a.lda == 0) a.lda = a.k;
+    if (a.ldd == 0) a.ldd = a.n;
+    const bool bf16 = a.weights_dt == UZU_DT_BF16;
+    static const bool no_tensor = getenv("UZU_DENSE_NO_TENSOR") != nullptr;
+    if (a.m <= DL_MAX_ROWS) {
+        dim3 grid((a.n + 7) / 8, a.batch);
+        if (bf16) launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, a);
+        else launch(cmd, "dense_rows_kernel", dense_rows_kernel<float>, grid, dim3(256), 0, a);
+        return;
+    }
+    if (bf16 && a.m >= 32 && !no_tensor) {
+        dim3 grid((a.n + TC_BN - 1) / TC_BN, (a.m + TC_BM - 1) / TC_BM, a.batch);
+        dense_tensor_kernel<<<grid, 128, 0, cmd->ctx->stream>>>(a);
+        after_launch(cmd, "dense_tensor_kernel");
+        return;
+    }
+    dim3 grid((a.n + DT_BN - 1) / DT_BN, (a.m + DT_BM - 1) / DT_BM, a.batch);
+    if (bf16) dense_tile_kernel<__nv_bfloat16><<<grid, 256, 0, cmd->ctx->stream>>>(a);
+    else dense_tile_kernel<float><<<grid, 256, 0, cmd->ctx->stream>>>(a);
+    after_launch(cmd, "dense_tile_kernel");
+}

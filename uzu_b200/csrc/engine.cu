@@ -289,12 +289,14 @@ struct Norm {
 };
 
 struct RopeCfg {
-    int kind = 0;  // 0 unscaled, 1 linear, 2 llama
+    int kind = 0;  // 0 unscaled, 1 linear, 2 llama, 3 interleaved pairs with optional YaRN blending (table rows are [pairs], already scaled)
     float base = 10000.0f, scaling_factor = 1.0f, low = 1.0f, high = 1.0f;
     uint32_t head_dim = 0, original_context_length = 0, max_sequence_length = 0;
+    bool yarn = false;          // kind 3: low / high hold the slow / fast rotation counts of the blend
+    uint32_t table_width() const { return kind == 3 ? head_dim / 2 : head_dim; }
     bool operator==(const RopeCfg& o) const {
         return kind == o.kind && base == o.base && scaling_factor == o.scaling_factor && low == o.low && high == o.high &&
-               head_dim == o.head_dim && original_context_length == o.original_context_length;
+               head_dim == o.head_dim && original_context_length == o.original_context_length && yarn == o.yarn;
     }
 };
 
@@ -318,11 +320,49 @@ struct DeltaNetLayer {
     float norm_epsilon = 1e-6f;
 };
 
+// ---- parallel-block family (dense weights in the engine's storage type, f32 residual stream) ----
+struct DenseMatrix {      // `count` matrices [rows, cols] (out, in) back to back: per-head or per-expert weights share one buffer
+    Buf w;
+    uint32_t rows = 0, cols = 0, count = 1;
+    uint64_t bytes = 0;
+    uint64_t stride() const { return (uint64_t)rows * cols; }
+};
+
+struct GeneralDeltaLayer {   // generalized delta rule mixer: decay and removal rate per key channel
+    DenseMatrix in;          // rows [receptance | key | value | rate | gate | decay latent]
+    DenseMatrix decay_up, out;
+    Buf rate_bias, decay_bias, norm_weight;   // f32 [heads * dim]
+    uint32_t heads = 0, dim = 0, decay_rank = 0;
+};
+
+struct LatentAttentionLayer {   // latent attention: normed query latent, shared normed kv latent + one rotated key part
+    DenseMatrix in;             // rows [query latent | kv latent | rotated key part | output gate]
+    DenseMatrix q_up, key_absorb /* heads x [rank, dim] = per-head key up-projection transposed */, value_up /* heads x [vdim, rank] */, out;
+    Buf q_norm, latent_norm;    // f32
+    uint32_t heads = 0, dim = 0, rot_dim = 0, vdim = 0, rank = 0, q_rank = 0;
+    float scale = 1.0f;
+    int rope_index = -1;
+};
+
+struct GatedMlp {               // clamped gated unit; dense, or experts picked per token id from a table
+    enum Kind { None, Dense, TableExperts } kind = None;
+    DenseMatrix gate_up /* experts x [2f, W]: gate rows then up rows */, down /* experts x [W, f] */;
+    Buf table;                  // i32 [vocab, top]
+    uint32_t f = 0, experts = 1, top = 1;
+    float limit = 0.0f;
+};
+
+enum MixerKind : uint32_t { MixAttention = 0, MixDeltaNet = 1, MixGeneralDelta = 2, MixLatentAttention = 3 };
+
 struct Layer {
-    bool is_attention = true;
+    bool is_attention = true;   // the mixer keeps a per-token cache whose length advances with the context (MixAttention, MixLatentAttention)
+    uint32_t kind = MixAttention;
     Norm pre_mixer, pre_mlp;
     AttentionLayer attn;
     DeltaNetLayer dn;
+    GeneralDeltaLayer gd;
+    LatentAttentionLayer la;
+    GatedMlp gmlp;
     Linear up, down;
     uint32_t hidden_dim = 0;
     uint32_t act = UZU_ACT_SILU;
@@ -401,6 +441,20 @@ struct uzu_engine {
     std::vector<Buf> rope_cos, rope_sin;  // [positions, rope_dim] f32
     uint32_t rope_positions = 0;
     std::vector<uzu_buffer*> owned;
+    // parallel-block family: x <- x + mixer(norm(x)) + mlp(norm(x)), f32 residual, grouped RMS norm, dense weights of type store_dt
+    bool parallel_block = false;
+    uint32_t store_dt = UZU_DT_BF16, norm_groups = 1;
+    float norm_eps = 1e-5f;
+    DenseMatrix pb_embed, pb_head;
+    Buf pb_final_norm;
+    struct PbScratch {
+        Buf resid, normed, proj, lat, wide, query, mixed, gated_mix, mix_out, gate_up, act, pair_out, ff_out, group_offsets, rows_map, pair_pos,
+            normed_rows, logits_f32, layer_dump;
+        uint32_t dump_rows = 0;
+        bool dump = false;
+    } pb;
+    // sequence slots: which entries of `seqs` are handed out (uzu_engine_slot_acquire / release)
+    std::vector<uint8_t> slot_used;
     // state
     std::vector<LayerState> state;
     uint32_t context_length = 0, snapshot_context = 0;
@@ -593,6 +647,35 @@ static RopeCfg parse_rope(const Json& j) {
 // PrecalculatedRoPE::precalculate (mixer/attention/rope.rs:13-114), evaluated for positions [0, count)
 static void rope_tables(const RopeCfg& c, uint32_t count, float* cosines, float* sines) {
     const uint32_t head_dim = c.head_dim, half = head_dim / 2;
+    if (c.kind == 3) {
+        // Interleaved pairs (2i, 2i+1), frequency f_i = base^(-2i/dims). YaRN: with where(t) = dims * ln(original / (2 pi t)) / (2 ln base),
+        // lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the
+        // frequency becomes f_i / factor * ramp_i + f_i * (1 - ramp_i) and cos / sin carry the factor 0.1 ln(factor) + 1. Frequencies are
+        // formed in double and rounded once; the angle position * frequency is an f32 product.
+        double lo = 0.0, hi = 0.0, mult = 1.0;
+        if (c.yarn) {
+            auto where = [&](double turns) {
+                return (double)head_dim * std::log((double)c.original_context_length / (2.0 * 3.14159265358979323846 * turns)) / (2.0 * std::log((double)c.base));
+            };
+            lo = std::max(std::floor(where((double)c.high)), 0.0);
+            hi = std::min(std::ceil(where((double)c.low)), (double)head_dim - 1.0);
+            mult = 0.1 * std::log((double)c.scaling_factor) + 1.0;
+        }
+        for (uint32_t i = 0; i < half; ++i) {
+            double f = std::pow((double)c.base, -2.0 * (double)i / (double)head_dim);
+            if (c.yarn) {
+                const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+                f = f / (double)c.scaling_factor * ramp + f * (1.0 - ramp);
+            }
+            const float ff = (float)f;
+            for (uint32_t t = 0; t < count; ++t) {
+                const float angle = (float)t * ff;
+                cosines[(size_t)t * half + i] = (float)(std::cos((double)angle) * mult);
+                sines[(size_t)t * half + i] = (float)(std::sin((double)angle) * mult);
+            }
+        }
+        return;
+    }
     for (uint32_t pair = 0; pair < half; ++pair) {
         const uint32_t channel = pair * 2;
         float inv = 1.0f / powf(c.base, (float)channel / (float)head_dim);
@@ -620,9 +703,31 @@ static void rope_tables(const RopeCfg& c, uint32_t count, float* cosines, float*
     }
 }
 
+static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std::string& dir);
+static void load_language_model_config(uzu_engine* e, const Json& cfg, const std::string& dir);
+
+// Model registry: config.json names its family, either by the reference's type tag or by an "architecture" string.
+struct ModelFamily {
+    const char* name;
+    bool (*matches)(const Json& cfg);
+    void (*load)(uzu_engine* e, const Json& cfg, const std::string& dir);
+};
+static const ModelFamily kModelFamilies[] = {
+    {"LanguageModelConfig", [](const Json& c) { const Json* t = c.get("type"); return t && t->str == "LanguageModelConfig"; }, load_language_model_config},
+    {"Punilix", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Punilix"; }, load_parallel_block_model},
+};
+
 static void load_model(uzu_engine* e, const std::string& dir) {
     Json cfg = parse_json(read_file(dir + "/config.json"));
-    if (cfg.type_tag() != "LanguageModelConfig") throw std::runtime_error("config.json: not a LanguageModelConfig");
+    for (const ModelFamily& f : kModelFamilies)
+        if (f.matches(cfg)) {
+            f.load(e, cfg, dir);
+            return;
+        }
+    throw std::runtime_error("config.json: not a LanguageModelConfig and no known \"architecture\"");
+}
+
+static void load_language_model_config(uzu_engine* e, const Json& cfg, const std::string& dir) {
     const Json& dec = cfg.at("decoder_config");
     const Json& tr = dec.at("transformer_config");
     e->model_dim = tr.at("model_dim").u32();
@@ -722,6 +827,7 @@ static void load_model(uzu_engine* e, const std::string& dir) {
         } else if (mty == "DeltaNetConfig") {
             if (e->tp_sharded) throw std::runtime_error("tensor parallelism covers attention mixers only");
             L.is_attention = false;
+            L.kind = MixDeltaNet;
             DeltaNetLayer& D = L.dn;
             D.num_heads = mc.at("num_heads").u32();
             D.num_groups = mc.at("num_groups").u32();
@@ -777,6 +883,58 @@ static void load_model(uzu_engine* e, const std::string& dir) {
     e->info.state_bytes_per_token = stb;
 }
 
+// State of one layer of one sequence, by mixer kind: a per-token cache (demand-paged where the device has virtual memory management)
+// or fixed-size recurrent state with its snapshot.
+static size_t storage_size(uint32_t dt) { return dt == UZU_DT_F32 ? 4 : 2; }
+
+static void alloc_layer_state(uzu_engine* e, const Layer& L, LayerState& S, uint32_t rows_total, bool sparse, bool zero) {
+    auto paged = [&](uzu_sparse_buffer*& sp, Buf& dense, uint64_t& ptr, size_t bytes) {
+        if (sparse) {
+            check(uzu_sparse_buffer_create(e->ctx, bytes, &sp));
+            ptr = uzu_sparse_buffer_gpu_ptr(sp);
+        } else {
+            dense = make_buf(e, bytes, UZU_BUFFER_DEVICE);
+            ptr = dense.ptr();
+        }
+    };
+    auto fixed = [&](Buf& b, size_t bytes) {
+        b = make_buf(e, bytes, UZU_BUFFER_DEVICE);
+        if (zero) cudaMemsetAsync((void*)b.ptr(), 0, bytes, e->ctx->stream);
+    };
+    switch (L.kind) {
+        case MixAttention: {
+            S.row_bytes = (size_t)L.attn.num_groups * L.attn.head_dim * 2;
+            paged(S.k_sparse, S.k_dense, S.keys, (size_t)rows_total * S.row_bytes);
+            paged(S.v_sparse, S.v_dense, S.values, (size_t)rows_total * S.row_bytes);
+            break;
+        }
+        case MixLatentAttention: {   // one row per token: [latent | rotated key part], shared by all heads; no separate values
+            S.row_bytes = (size_t)(L.la.rank + L.la.rot_dim) * storage_size(e->store_dt);
+            paged(S.k_sparse, S.k_dense, S.keys, (size_t)rows_total * S.row_bytes);
+            break;
+        }
+        case MixDeltaNet: {
+            const DeltaNetLayer& D = L.dn;
+            S.conv_bytes = (size_t)D.conv_dim * (D.kernel_size - 1) * 4;
+            S.ssm_bytes = (size_t)D.num_heads * D.value_head_dim * D.head_dim * 4;
+            fixed(S.conv_state, S.conv_bytes);
+            fixed(S.ssm_state, S.ssm_bytes);
+            S.conv_snapshot = make_buf(e, S.conv_bytes, UZU_BUFFER_DEVICE);
+            S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
+            break;
+        }
+        case MixGeneralDelta: {      // f32 [heads, dim, dim], no convolution window
+            S.ssm_bytes = (size_t)L.gd.heads * L.gd.dim * L.gd.dim * 4;
+            fixed(S.ssm_state, S.ssm_bytes);
+            S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
+            break;
+        }
+        default: throw std::runtime_error("unknown mixer kind");
+    }
+}
+
+static void create_parallel_block_scratch(uzu_engine* e);
+
 static void create_state_and_scratch(uzu_engine* e) {
     const uint32_t H = e->model_dim, V = e->vocab;
     uint32_t max_ctx = e->opts.max_context_length ? e->opts.max_context_length : 8192;
@@ -788,35 +946,16 @@ static void create_state_and_scratch(uzu_engine* e) {
     uint32_t max_qkv = 0, max_qd = 0, max_f = 0, max_proj = 0, max_vd = 0, max_heads = 0, max_hd = 0;
     for (size_t i = 0; i < e->layers.size(); ++i) {
         Layer& L = e->layers[i];
-        LayerState& S = e->state[i];
+        alloc_layer_state(e, L, e->state[i], rows_total, sparse, false);
         max_f = std::max(max_f, L.hidden_dim);
-        if (L.is_attention) {
+        if (L.kind == MixAttention) {
             const AttentionLayer& A = L.attn;
-            S.row_bytes = (size_t)A.num_groups * A.head_dim * 2;
-            const size_t bytes = (size_t)rows_total * S.row_bytes;
-            if (sparse) {
-                check(uzu_sparse_buffer_create(e->ctx, bytes, &S.k_sparse));
-                check(uzu_sparse_buffer_create(e->ctx, bytes, &S.v_sparse));
-                S.keys = uzu_sparse_buffer_gpu_ptr(S.k_sparse);
-                S.values = uzu_sparse_buffer_gpu_ptr(S.v_sparse);
-            } else {
-                S.k_dense = make_buf(e, bytes, UZU_BUFFER_DEVICE);
-                S.v_dense = make_buf(e, bytes, UZU_BUFFER_DEVICE);
-                S.keys = S.k_dense.ptr();
-                S.values = S.v_dense.ptr();
-            }
             max_qkv = std::max(max_qkv, (A.num_heads + 2 * A.num_groups) * A.head_dim);
             max_qd = std::max(max_qd, A.num_heads * A.head_dim);
             max_heads = std::max(max_heads, A.num_heads);
             max_hd = std::max(max_hd, A.head_dim);
-        } else {
+        } else if (L.kind == MixDeltaNet) {
             const DeltaNetLayer& D = L.dn;
-            S.conv_bytes = (size_t)D.conv_dim * (D.kernel_size - 1) * 4;
-            S.ssm_bytes = (size_t)D.num_heads * D.value_head_dim * D.head_dim * 4;
-            S.conv_state = make_buf(e, S.conv_bytes, UZU_BUFFER_DEVICE);
-            S.ssm_state = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
-            S.conv_snapshot = make_buf(e, S.conv_bytes, UZU_BUFFER_DEVICE);
-            S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
             max_proj = std::max(max_proj, D.total_proj_dim);
             max_vd = std::max(max_vd, D.value_dim);
         }
@@ -857,7 +996,7 @@ static void create_state_and_scratch(uzu_engine* e) {
     // RoPE tables for every position the state can hold
     e->rope_positions = rows_total;
     for (auto& rc : e->ropes) {
-        std::vector<float> cosv((size_t)rows_total * rc.head_dim), sinv((size_t)rows_total * rc.head_dim);
+        std::vector<float> cosv((size_t)rows_total * rc.table_width()), sinv((size_t)rows_total * rc.table_width());
         rope_tables(rc, rows_total, cosv.data(), sinv.data());
         Buf c = dev(cosv.size() * 4), s = dev(sinv.size() * 4);
         cudaMemcpy((void*)c.ptr(), cosv.data(), cosv.size() * 4, cudaMemcpyHostToDevice);
@@ -890,42 +1029,15 @@ static void create_state_and_scratch(uzu_engine* e) {
     }
     cudaEventCreateWithFlags(&e->step_events[0], cudaEventDisableTiming);
     cudaEventCreateWithFlags(&e->step_events[1], cudaEventDisableTiming);
+    create_parallel_block_scratch(e);
 }
 
-// One more independent sequence state (KV caches, DeltaNet states) with the same geometry as e->state: multi-sequence batched decode.
+// One more independent sequence state (KV caches, recurrent states) with the same geometry as e->state: multi-sequence batched decode, slots.
 static void alloc_sequence_state(uzu_engine* e, std::vector<LayerState>& st) {
     const uint32_t rows_total = e->max_context + MAX_ROWS;
     const bool sparse = (uzu_context_device_capabilities(e->ctx) & UZU_CAP_SPARSE_BUFFERS) != 0;
     st.assign(e->layers.size(), LayerState{});
-    for (size_t i = 0; i < e->layers.size(); ++i) {
-        const Layer& L = e->layers[i];
-        LayerState& S = st[i];
-        if (L.is_attention) {
-            S.row_bytes = (size_t)L.attn.num_groups * L.attn.head_dim * 2;
-            const size_t bytes = (size_t)rows_total * S.row_bytes;
-            if (sparse) {
-                check(uzu_sparse_buffer_create(e->ctx, bytes, &S.k_sparse));
-                check(uzu_sparse_buffer_create(e->ctx, bytes, &S.v_sparse));
-                S.keys = uzu_sparse_buffer_gpu_ptr(S.k_sparse);
-                S.values = uzu_sparse_buffer_gpu_ptr(S.v_sparse);
-            } else {
-                S.k_dense = make_buf(e, bytes, UZU_BUFFER_DEVICE);
-                S.v_dense = make_buf(e, bytes, UZU_BUFFER_DEVICE);
-                S.keys = S.k_dense.ptr();
-                S.values = S.v_dense.ptr();
-            }
-        } else {
-            const DeltaNetLayer& D = L.dn;
-            S.conv_bytes = (size_t)D.conv_dim * (D.kernel_size - 1) * 4;
-            S.ssm_bytes = (size_t)D.num_heads * D.value_head_dim * D.head_dim * 4;
-            S.conv_state = make_buf(e, S.conv_bytes, UZU_BUFFER_DEVICE);
-            S.ssm_state = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
-            S.conv_snapshot = make_buf(e, S.conv_bytes, UZU_BUFFER_DEVICE);
-            S.ssm_snapshot = make_buf(e, S.ssm_bytes, UZU_BUFFER_DEVICE);
-            cudaMemsetAsync((void*)S.conv_state.ptr(), 0, S.conv_bytes, e->ctx->stream);
-            cudaMemsetAsync((void*)S.ssm_state.ptr(), 0, S.ssm_bytes, e->ctx->stream);
-        }
-    }
+    for (size_t i = 0; i < e->layers.size(); ++i) alloc_layer_state(e, e->layers[i], st[i], rows_total, sparse, true);
 }
 
 // TransformerState::prepare (state.rs:141-172): make sure KV pages for rows [0, rows) are mapped
@@ -938,12 +1050,17 @@ static void state_prepare(uzu_engine* e, uint32_t rows_needed) {
         std::vector<uint32_t> pages;
         for (uint32_t p = S.mapped_pages; p < need; ++p) pages.push_back(p);
         check(uzu_sparse_buffer_map(S.k_sparse, pages.data(), pages.size()));
-        check(uzu_sparse_buffer_map(S.v_sparse, pages.data(), pages.size()));
+        if (S.v_sparse) check(uzu_sparse_buffer_map(S.v_sparse, pages.data(), pages.size()));
         S.mapped_pages = need;
     }
 }
 
 static void upload_decode_state(uzu_engine* e);
+
+static void zero_recurrent_state(uzu_engine* e, LayerState& S) {
+    if (S.conv_state.b) cudaMemsetAsync((void*)S.conv_state.ptr(), 0, S.conv_bytes, e->ctx->stream);
+    if (S.ssm_state.b) cudaMemsetAsync((void*)S.ssm_state.ptr(), 0, S.ssm_bytes, e->ctx->stream);
+}
 
 static void reset_state(uzu_engine* e) {
     cudaStreamSynchronize(e->ctx->stream);
@@ -952,10 +1069,7 @@ static void reset_state(uzu_engine* e) {
     e->trie_pending = 0;
     for (auto& S : e->state) {
         S.length = 0;
-        if (S.conv_state.b) {
-            cudaMemsetAsync((void*)S.conv_state.ptr(), 0, S.conv_bytes, e->ctx->stream);
-            cudaMemsetAsync((void*)S.ssm_state.ptr(), 0, S.ssm_bytes, e->ctx->stream);
-        }
+        zero_recurrent_state(e, S);
     }
     e->steps_issued = e->steps_returned = 0;
     cudaMemsetAsync((void*)e->token_ids.ptr(), 0, 4, e->ctx->stream);
@@ -1170,7 +1284,17 @@ static uint64_t encode_delta_net(uzu_engine* e, uzu_command_buffer* cmd, const L
 }
 
 // Decoder::encode for `m` tokens already in e->token_ids; logits for rows [row_begin, row_end) land in e->logits.
+static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx& pc, uint32_t row_begin, uint32_t row_end);
+static void encode_parallel_block_readout(uzu_engine* e, uzu_command_buffer* cmd, uint32_t row_begin, uint32_t row_end);
+
+// The tail of Decoder::encode: output norm + readout (+ logit transform) of rows [row_begin, row_end) of the pass's final hidden state.
+static void encode_readout_tail(uzu_engine* e, uzu_command_buffer* cmd, uint32_t row_begin, uint32_t row_end);
+
 static void encode_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx& pc, uint32_t row_begin, uint32_t row_end) {
+    if (e->parallel_block) {
+        encode_parallel_block_decoder(e, cmd, pc, row_begin, row_end);
+        return;
+    }
     const uint32_t m = pc.m, H = e->model_dim;
     // embedding lookup (embedding.rs:345-372)
     if (e->in_emb.w.prologue == UZU_B_FULL_PRECISION) {
@@ -1202,14 +1326,25 @@ static void encode_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx
         encode_row_parallel(e, cmd, L.down, e->gated.ptr(), m, e->hidden_a.ptr());
         hidden = e->hidden_a.ptr();
     }
+    encode_readout_tail(e, cmd, row_begin, row_end);
+}
+
+static void encode_readout_tail(uzu_engine* e, uzu_command_buffer* cmd, uint32_t row_begin, uint32_t row_end) {
     if (row_end <= row_begin) return;
-    const uint32_t rows = row_end - row_begin;
+    if (e->parallel_block) {
+        encode_parallel_block_readout(e, cmd, row_begin, row_end);
+        return;
+    }
+    const uint32_t rows = row_end - row_begin, H = e->model_dim;
+    const uint64_t hidden = e->hidden_a.ptr();     // every layer leaves its output there
     // output_norm over the requested rows, residual add into the same rows of the shortcut (transformer.rs:317-323)
     encode_norm(cmd, e->out_norm, hidden + (size_t)row_begin * H * 2, e->normed_out.ptr(), e->shortcut.ptr() + (size_t)row_begin * H * 2, ShortcutAdd, rows);
     encode_readout(e, cmd, e->normed_out.ptr(), rows);
     if (e->has_logit_scale || e->has_logit_soft_cap)
         uzu_logit_transform_encode(cmd, e->logits.ptr(), rows * e->vocab, e->has_logit_scale ? e->logit_scale : 1.0f, e->logit_soft_cap, e->has_logit_soft_cap);
 }
+
+#include "engine_parallel_block.inl"
 
 // ---- fused decode step (m = 1): norm / gated-act / sigmoid-gate launches folded into the consuming GEMV ---------------------
 static uzu_matmul_args linear_args(const Linear& l, uint64_t a, uint32_t m, uint64_t d) {
@@ -2134,8 +2269,9 @@ uzu_status uzu_engine_create(uzu_context* ctx, const char* model_dir, const uzu_
         load_model(e, model_dir);
         create_state_and_scratch(e);
         reset_state(e);
-        e->fused_ok = e->opts.fused_decode && getenv("UZU_NO_FUSED") == nullptr && fused_decode_supported(e);
-        if (e->opts.fused_decode) {                   // the persistent decode kernel is the fused path's next step: one launch per token
+        e->fused_ok = !e->parallel_block && e->opts.fused_decode && getenv("UZU_NO_FUSED") == nullptr && fused_decode_supported(e);
+        if (e->parallel_block) e->mega.why = "the persistent decode kernel does not cover the parallel-block family";
+        if (e->opts.fused_decode && !e->parallel_block) {                   // the persistent decode kernel is the fused path's next step: one launch per token
             build_mega(e);
             calibrate_decode_path(e);
         }
@@ -2183,11 +2319,10 @@ uint32_t uzu_engine_context_length(const uzu_engine* e) { return e ? e->context_
 uzu_status uzu_engine_snapshot(uzu_engine* e) {
     UZU_ENGINE_TRY({
         cudaStream_t s = e->ctx->stream;
-        for (auto& S : e->state)
-            if (S.conv_state.b) {
-                cudaMemcpyAsync((void*)S.conv_snapshot.ptr(), (void*)S.conv_state.ptr(), S.conv_bytes, cudaMemcpyDeviceToDevice, s);
-                cudaMemcpyAsync((void*)S.ssm_snapshot.ptr(), (void*)S.ssm_state.ptr(), S.ssm_bytes, cudaMemcpyDeviceToDevice, s);
-            }
+        for (auto& S : e->state) {
+            if (S.conv_state.b) cudaMemcpyAsync((void*)S.conv_snapshot.ptr(), (void*)S.conv_state.ptr(), S.conv_bytes, cudaMemcpyDeviceToDevice, s);
+            if (S.ssm_state.b) cudaMemcpyAsync((void*)S.ssm_snapshot.ptr(), (void*)S.ssm_state.ptr(), S.ssm_bytes, cudaMemcpyDeviceToDevice, s);
+        }
         cudaMemcpyAsync((void*)e->snapshot_token.ptr(), (void*)e->token_ids.ptr(), 4, cudaMemcpyDeviceToDevice, s);
         cudaStreamSynchronize(s);
         e->snapshot_context = e->context_length;
@@ -2200,8 +2335,8 @@ uzu_status uzu_engine_restore(uzu_engine* e) {
         cudaStreamSynchronize(s);
         for (size_t i = 0; i < e->state.size(); ++i) {
             auto& S = e->state[i];
-            if (S.conv_state.b) {
-                cudaMemcpyAsync((void*)S.conv_state.ptr(), (void*)S.conv_snapshot.ptr(), S.conv_bytes, cudaMemcpyDeviceToDevice, s);
+            if (S.ssm_state.b) {
+                if (S.conv_state.b) cudaMemcpyAsync((void*)S.conv_state.ptr(), (void*)S.conv_snapshot.ptr(), S.conv_bytes, cudaMemcpyDeviceToDevice, s);
                 cudaMemcpyAsync((void*)S.ssm_state.ptr(), (void*)S.ssm_snapshot.ptr(), S.ssm_bytes, cudaMemcpyDeviceToDevice, s);
             } else {
                 S.length = e->snapshot_context;   // KV rows beyond the snapshot are simply overwritten
@@ -2296,14 +2431,14 @@ uzu_status uzu_engine_forward(uzu_engine* e, const uint32_t* tokens, uint32_t co
 // token per node) and later compacts the KV rows of the accepted path (TransformerState::encode_accept).
 int uzu_engine_speculation_supported(const uzu_engine* e) {
     // Mixer::speculation_supported: attention always, DeltaNet only with a tree-verify core (delta_net.rs:442-444) -- not built here
-    return e && !has_delta(e) ? 1 : 0;
+    return e && !has_delta(e) && !e->parallel_block ? 1 : 0;
 }
 
 uzu_status uzu_engine_trie_pass(uzu_engine* e, const uint32_t* tokens, const uzu_trie_node* nodes, const uint64_t* seeds, uint32_t count,
                                 const uzu_sampling_method* sampling, uint32_t* out_tokens, uint16_t* out_logits) {
     UZU_ENGINE_TRY({
         if (!tokens || !nodes || count == 0 || count > MAX_TRIE) throw std::runtime_error("trie_pass: 1..16 nodes");
-        if (has_delta(e)) throw std::runtime_error("trie_pass: DeltaNet tree verification is not supported (speculation_supported == 0)");
+        if (has_delta(e) || e->parallel_block) throw std::runtime_error("trie_pass: tree verification is not supported for this model (speculation_supported == 0)");
         if (e->trie_pending) throw std::runtime_error("trie_pass: the previous speculation pass was not accepted");
         if (e->steps_returned != e->steps_issued) throw std::runtime_error("trie_pass: flush() the in-flight decode steps first");
         // a linearized trie: depth-first order, node i's subtree = [trie_start, trie_end] = [i, >= i], height = depth (trie.rs:158-178)
@@ -2669,9 +2804,106 @@ static void run_batch_step(uzu_engine* e, bool chain) {
 
 }  // namespace uzu
 
+
+// ---- sequence slots + row-list forward --------------------------------------------------------------------------------------------
+uzu_status uzu_engine_slot_acquire(uzu_engine* e, uint32_t* out_slot) {
+    UZU_ENGINE_TRY({
+        if (!out_slot) throw std::runtime_error("slot_acquire: null output");
+        if (e->batch_graph) throw std::runtime_error("slot_acquire: a batched decode is active");
+        e->slot_used.resize(e->seqs.size(), 0);
+        uint32_t slot = 0;
+        while (slot < e->slot_used.size() && e->slot_used[slot]) ++slot;
+        if (slot == e->seqs.size()) {
+            if (slot >= 64) throw std::runtime_error("slot_acquire: all 64 slots are in use");
+            e->seqs.emplace_back();
+            alloc_sequence_state(e, e->seqs.back().layers);
+            e->slot_used.push_back(0);
+        }
+        uzu_engine::Sequence& q = e->seqs[slot];       // a reused slot keeps its mapped pages and buffers; its contents are reset
+        q.context_length = 0;
+        for (auto& S : q.layers) {
+            S.length = 0;
+            zero_recurrent_state(e, S);
+        }
+        cudaStreamSynchronize(e->ctx->stream);
+        e->slot_used[slot] = 1;
+        *out_slot = slot;
+    });
+}
+
+uzu_status uzu_engine_slot_release(uzu_engine* e, uint32_t slot) {
+    UZU_ENGINE_TRY({
+        if (slot >= e->slot_used.size() || !e->slot_used[slot]) throw std::runtime_error("slot_release: slot is not in use");
+        e->slot_used[slot] = 0;
+    });
+}
+
+uzu_status uzu_engine_forward_rows(uzu_engine* e, uint32_t slot, const uint32_t* tokens, uint32_t count, const uint32_t* rows, uint32_t nrows,
+                                   float* out_logits) {
+    UZU_ENGINE_TRY({
+        if (!tokens || count == 0) throw std::runtime_error("forward_rows: empty input");
+        if (nrows && (!rows || !out_logits)) throw std::runtime_error("forward_rows: null row list / output");
+        for (uint32_t i = 0; i < nrows; ++i)
+            if (rows[i] >= count || (i && rows[i] <= rows[i - 1])) throw std::runtime_error("forward_rows: rows must be ascending indices into the tokens");
+        if (slot != UZU_MAIN_SLOT && (slot >= e->slot_used.size() || !e->slot_used[slot])) throw std::runtime_error("forward_rows: slot is not in use");
+        std::unique_ptr<SeqSwap> sw;
+        if (slot != UZU_MAIN_SLOT) sw.reset(new SeqSwap(e, slot));
+        const size_t V = e->vocab;
+        std::vector<uint16_t> half;
+        uint32_t next = 0;
+        for (uint32_t s0 = 0; s0 < count; s0 += MAX_ROWS) {
+            const uint32_t n = std::min(MAX_ROWS, count - s0);
+            run_pass(e, tokens + s0, n, 0, 0, false);
+            while (next < nrows && rows[next] < s0 + n) {     // contiguous runs of wanted rows, at most logits_rows at a time
+                uint32_t end = next + 1;
+                while (end < nrows && rows[end] == rows[end - 1] + 1 && rows[end] < s0 + n && end - next < e->logits_rows) ++end;
+                const uint32_t rb = rows[next] - s0, re = rb + (end - next);
+                CmdGuard g(e->ctx, "readout");
+                check(uzu_command_buffer_start_encoding(g.c));
+                encode_readout_tail(e, g.c, rb, re);
+                run_cmd_to_completion(e, g.c);
+                float* dst = out_logits + (size_t)next * V;
+                if (e->parallel_block) {
+                    cudaMemcpy(dst, (void*)e->pb.logits_f32.ptr(), (size_t)(end - next) * V * 4, cudaMemcpyDeviceToHost);
+                } else {
+                    half.resize((size_t)(end - next) * V);
+                    cudaMemcpy(half.data(), (void*)e->logits.ptr(), half.size() * 2, cudaMemcpyDeviceToHost);
+                    for (size_t i = 0; i < half.size(); ++i) {
+                        const uint32_t bits = (uint32_t)half[i] << 16;
+                        memcpy(dst + i, &bits, 4);
+                    }
+                }
+                next = end;
+            }
+        }
+        if (slot == UZU_MAIN_SLOT) upload_decode_state(e);
+    });
+}
+
+uzu_status uzu_engine_debug_layer_outputs(uzu_engine* e, uint32_t enable, float* out, uint32_t capacity_floats, uint32_t* out_count) {
+    UZU_ENGINE_TRY({
+        if (!e->parallel_block) throw std::runtime_error("debug_layer_outputs: only the parallel-block family keeps an f32 residual stream");
+        auto& P = e->pb;
+        P.dump = enable != 0;
+        if (P.dump && !P.layer_dump.b) P.layer_dump = make_buf(e, (size_t)e->layers.size() * MAX_ROWS * e->model_dim * 4, UZU_BUFFER_DEVICE);
+        const uint32_t W = e->model_dim, rows = P.dump_rows;
+        const size_t total = (size_t)e->layers.size() * rows * W;
+        if (out_count) *out_count = (uint32_t)total;
+        if (out && total) {
+            if (capacity_floats < total) throw std::runtime_error("debug_layer_outputs: output too small");
+            cudaStreamSynchronize(e->ctx->stream);
+            for (size_t i = 0; i < e->layers.size(); ++i)
+                cudaMemcpy(out + i * rows * W, (void*)(P.layer_dump.ptr() + (uint64_t)i * MAX_ROWS * W * 4), (size_t)rows * W * 4, cudaMemcpyDeviceToHost);
+        }
+    });
+}
+
 uzu_status uzu_engine_batch_begin(uzu_engine* e, uint32_t sequences) {
     UZU_ENGINE_TRY({
         if (sequences == 0 || sequences > 16) throw std::runtime_error("batch_begin: 1..16 sequences (the m <= 16 GEMV rows)");
+        if (e->parallel_block) throw std::runtime_error("batch_begin: the shared-weight batched step is not built for the parallel-block family (use sequence slots)");
+        for (uint8_t u : e->slot_used)
+            if (u) throw std::runtime_error("batch_begin: sequence slots are in use");
         if (e->tp_sharded) throw std::runtime_error("batch_begin: not combined with tensor parallelism yet");
         if (e->sampling.kind == UZU_SAMPLING_STOCHASTIC) throw std::runtime_error("batch decode samples greedily (per-row seeds are not wired yet)");
         if (e->logits_rows < sequences) throw std::runtime_error("batch_begin: logits scratch too small");
@@ -2707,10 +2939,7 @@ uzu_status uzu_engine_batch_begin(uzu_engine* e, uint32_t sequences) {
             q.context_length = 0;
             for (auto& S : q.layers) {
                 S.length = 0;
-                if (S.conv_state.b) {
-                    cudaMemsetAsync((void*)S.conv_state.ptr(), 0, S.conv_bytes, e->ctx->stream);
-                    cudaMemsetAsync((void*)S.ssm_state.ptr(), 0, S.ssm_bytes, e->ctx->stream);
-                }
+                zero_recurrent_state(e, S);
             }
         }
         cudaStreamSynchronize(e->ctx->stream);
@@ -2789,6 +3018,7 @@ uint32_t uzu_engine_batch_context_length(const uzu_engine* e, uint32_t sequence)
 
 uzu_status uzu_engine_time_linears_select(uzu_engine* e, uint32_t iters, uint32_t select, double* out_seconds, uint64_t* out_launches) {
     UZU_ENGINE_TRY({
+        if (e->parallel_block) throw std::runtime_error("uzu_engine_time_linears_select: not built for the parallel-block family");
         cudaStream_t s = e->ctx->stream;
         CmdGuard g(e->ctx, "linears");
         g.c->state = uzu_command_buffer::Encoding;
@@ -2861,6 +3091,7 @@ uzu_status uzu_engine_time_linears_select(uzu_engine* e, uint32_t iters, uint32_
 
 uzu_status uzu_engine_time_prefill_linears(uzu_engine* e, uint32_t m, uint32_t iters, double* out_seconds, double* out_flops) {
     UZU_ENGINE_TRY({
+        if (e->parallel_block) throw std::runtime_error("uzu_engine_time_prefill_linears: not built for the parallel-block family");
         if (m == 0 || m > MAX_ROWS || iters == 0) throw std::runtime_error("time_prefill_linears: m must be in 1..1024, iters > 0");
         cudaStream_t s = e->ctx->stream;
         CmdGuard g(e->ctx, "prefill linears");

@@ -1,0 +1,459 @@
+// Parallel-block family (Punilix) inside the host engine: configuration, weights, scratch and the encoding of one pass. Included by
+// engine.cu; the pass driver, the state / cache manager, sampling, CUDA-graph decode and the sequence slots are the engine's own.
+//
+//   x = embed[token]                                                      (f32 residual stream)
+//   per layer:  h = group_rms(x);  x <- x + mixer(h) + mlp(h)             (one norm feeds both sublayers)
+//   logits = cap * tanh(head . group_rms(x) / cap)
+//
+// config.json: "architecture", "width", "vocab", "norm": {"eps", "groups"}, "logit_softcap", "layers": [{"type", "mixer": {...}, "mlp"}].
+// Tensors: embed, head, final.norm, l<i>.norm1, l<i>.mix.*, l<i>.mlp.* (bf16 or f32 floats, i32 tables); linear weights are [out, in].
+// Weights are assembled on the host at load: projections that read the same input are stacked into one matrix, per-head key
+// up-projections are transposed for the absorbed form, expert matrices lie back to back. Storage is bf16, or f32 when the engine was
+// created with storage_f32 (then every product is a plain f32 multiply-add).
+
+namespace {
+
+struct HostTensor {
+    std::vector<float> v;
+    std::vector<uint64_t> shape;
+    uint64_t rows() const { return shape.empty() ? 0 : shape[0]; }
+    uint64_t cols() const { return shape.size() < 2 ? 1 : shape[1]; }
+};
+
+static HostTensor read_floats(ParameterLoader& pl, const std::string& name, const std::vector<uint64_t>& shape) {
+    auto it = pl.tensors.find(name);
+    if (it == pl.tensors.end()) throw std::runtime_error("missing tensor '" + name + "'");
+    const std::string dt = it->second.dtype;
+    if (dt != "BF16" && dt != "F32") throw std::runtime_error("tensor '" + name + "' has dtype " + dt + ", expected BF16 or F32");
+    const TensorInfo& t = pl.validate(name, shape, dt);
+    HostTensor h;
+    h.shape = shape;
+    uint64_t n = 1;
+    for (auto d : shape) n *= d;
+    h.v.resize(n);
+    if (dt == "F32") {
+        pl.read_into(t, h.v.data());
+    } else {
+        std::vector<uint16_t> raw(n);
+        pl.read_into(t, raw.data());
+        for (uint64_t i = 0; i < n; ++i) {
+            const uint32_t bits = (uint32_t)raw[i] << 16;
+            memcpy(&h.v[i], &bits, 4);
+        }
+    }
+    return h;
+}
+
+static uint16_t f32_to_bf16_rne(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+
+static Buf upload_f32(uzu_engine* e, const std::vector<float>& v) {
+    Buf b = make_buf(e, std::max<size_t>(v.size() * 4, 16), UZU_BUFFER_DEVICE);
+    cudaMemcpy((void*)b.ptr(), v.data(), v.size() * 4, cudaMemcpyHostToDevice);
+    return b;
+}
+
+// `count` matrices [rows, cols] back to back, in the engine's storage type
+static DenseMatrix upload_matrix(uzu_engine* e, const std::vector<float>& v, uint32_t rows, uint32_t cols, uint32_t count = 1) {
+    if (v.size() != (size_t)rows * cols * count) throw std::runtime_error("internal: matrix assembly size mismatch");
+    DenseMatrix m;
+    m.rows = rows; m.cols = cols; m.count = count;
+    m.bytes = v.size() * storage_size(e->store_dt);
+    m.w = make_buf(e, std::max<size_t>(m.bytes, 16), UZU_BUFFER_DEVICE);
+    if (e->store_dt == UZU_DT_F32) {
+        cudaMemcpy((void*)m.w.ptr(), v.data(), m.bytes, cudaMemcpyHostToDevice);
+    } else {
+        std::vector<uint16_t> h(v.size());
+        for (size_t i = 0; i < v.size(); ++i) h[i] = f32_to_bf16_rne(v[i]);
+        cudaMemcpy((void*)m.w.ptr(), h.data(), m.bytes, cudaMemcpyHostToDevice);
+    }
+    return m;
+}
+
+static void append(std::vector<float>& dst, const HostTensor& t) { dst.insert(dst.end(), t.v.begin(), t.v.end()); }
+
+static uint32_t cfg_u32(const Json& j, const char* key) {
+    const Json& v = j.at(key);
+    if (v.type != Json::Num || v.num < 0 || v.num != std::floor(v.num) || v.num > 4294967295.0) throw std::runtime_error(std::string("config: '") + key + "' must be a non-negative integer");
+    return (uint32_t)v.num;
+}
+
+}  // namespace
+
+static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std::string& dir) {
+    if (e->opts.tp_size > 1) throw std::runtime_error("tensor parallelism is not built for the parallel-block family");
+    e->parallel_block = true;
+    e->store_dt = e->opts.storage_f32 ? UZU_DT_F32 : UZU_DT_BF16;
+    const uint32_t W = e->model_dim = cfg_u32(cfg, "width");
+    const uint32_t V = e->vocab = cfg_u32(cfg, "vocab");
+    const Json& nc = cfg.at("norm");
+    e->norm_eps = (float)nc.at("eps").number();
+    e->norm_groups = cfg_u32(nc, "groups");
+    if (e->norm_groups == 0 || W % e->norm_groups) throw std::runtime_error("config: width is not divisible into norm.groups parts");
+    if (const Json* cap = cfg.get("logit_softcap")) {
+        if (!cap->is_null()) { e->has_logit_soft_cap = true; e->logit_soft_cap = (float)cap->number(); }
+    }
+    ParameterLoader pl(dir + "/model.safetensors");
+    e->pb_embed = upload_matrix(e, read_floats(pl, "embed", {V, W}).v, V, W);
+    e->pb_head = upload_matrix(e, read_floats(pl, "head", {V, W}).v, V, W);
+    e->pb_final_norm = upload_f32(e, read_floats(pl, "final.norm", {W}).v);
+    uint64_t wbytes = e->pb_head.bytes, kvb = 0, stb = 0;
+    uint32_t n_cache = 0, n_rec = 0;
+    const auto& lcs = cfg.at("layers").arr;
+    e->layers.resize(lcs.size());
+    for (size_t i = 0; i < lcs.size(); ++i) {
+        const Json& lc = lcs[i];
+        Layer& L = e->layers[i];
+        const std::string p = "l" + std::to_string(i) + ".";
+        L.pre_mixer.present = true;
+        L.pre_mixer.n = W;
+        L.pre_mixer.cfg.epsilon = e->norm_eps;
+        L.pre_mixer.scales = upload_f32(e, read_floats(pl, p + "norm1", {W}).v);
+        const std::string type = lc.at("type").str;
+        const Json& mc = lc.at("mixer");
+        if (type == "general_delta") {
+            L.kind = MixGeneralDelta;
+            L.is_attention = false;
+            GeneralDeltaLayer& G = L.gd;
+            G.heads = cfg_u32(mc, "heads");
+            G.dim = cfg_u32(mc, "dim");
+            if (G.heads == 0 || G.dim == 0 || G.dim > 512) throw std::runtime_error(p + "mix: head size must be in 1..512");
+            const uint32_t HD = G.heads * G.dim;
+            auto it = pl.tensors.find(p + "mix.w1");
+            if (it == pl.tensors.end() || it->second.shape.size() != 2) throw std::runtime_error("missing tensor '" + p + "mix.w1'");
+            G.decay_rank = (uint32_t)it->second.shape[0];
+            std::vector<float> in;
+            for (const char* nm : {"r", "k", "v", "a", "g"}) append(in, read_floats(pl, p + "mix." + nm, {HD, W}));
+            append(in, read_floats(pl, p + "mix.w1", {G.decay_rank, W}));
+            G.in = upload_matrix(e, in, 5 * HD + G.decay_rank, W);
+            G.decay_up = upload_matrix(e, read_floats(pl, p + "mix.w2", {HD, G.decay_rank}).v, HD, G.decay_rank);
+            G.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, HD}).v, W, HD);
+            G.rate_bias = upload_f32(e, read_floats(pl, p + "mix.a.b", {HD}).v);
+            G.decay_bias = upload_f32(e, read_floats(pl, p + "mix.w0", {HD}).v);
+            G.norm_weight = upload_f32(e, read_floats(pl, p + "mix.norm", {HD}).v);
+            wbytes += G.in.bytes + G.decay_up.bytes + G.out.bytes;
+            stb += 2ull * G.heads * G.dim * G.dim * 4;
+            n_rec++;
+        } else if (type == "latent_attention") {
+            L.kind = MixLatentAttention;
+            L.is_attention = true;
+            LatentAttentionLayer& A = L.la;
+            A.heads = cfg_u32(mc, "heads");
+            A.dim = cfg_u32(mc, "dim");
+            A.rot_dim = cfg_u32(mc, "rot_dim");
+            A.vdim = cfg_u32(mc, "vdim");
+            A.rank = cfg_u32(mc, "kv_rank");
+            A.q_rank = cfg_u32(mc, "q_rank");
+            A.scale = (float)mc.at("scale").number();
+            if (A.heads == 0 || A.rank == 0 || A.rank > 512 || A.vdim == 0 || A.q_rank == 0) throw std::runtime_error(p + "mix: latent size must be in 1..512, heads / vdim / q_rank non-zero");
+            if (A.rot_dim) {
+                const Json& rot = mc.at("rot");
+                RopeCfg rc;
+                rc.kind = 3;
+                rc.base = (float)rot.at("base").number();
+                rc.head_dim = cfg_u32(rot, "dims");
+                rc.max_sequence_length = 0xFFFFFFFFu;
+                if (rc.head_dim % 2 || rc.head_dim > A.rot_dim) throw std::runtime_error(p + "mix: rot.dims must be even and at most rot_dim");
+                const Json* sc = rot.get("scaling");
+                if (sc && !sc->is_null()) {
+                    rc.yarn = true;
+                    rc.scaling_factor = (float)sc->at("factor").number();
+                    rc.original_context_length = cfg_u32(*sc, "original");
+                    rc.high = (float)sc->at("fast").number();
+                    rc.low = (float)sc->at("slow").number();
+                }
+                int idx = -1;
+                for (size_t r = 0; r < e->ropes.size(); ++r)
+                    if (e->ropes[r] == rc) idx = (int)r;
+                if (idx < 0) { e->ropes.push_back(rc); idx = (int)e->ropes.size() - 1; }
+                A.rope_index = idx;
+            }
+            const uint32_t qd = A.dim + A.rot_dim;
+            std::vector<float> in;
+            append(in, read_floats(pl, p + "mix.dq", {A.q_rank, W}));
+            append(in, read_floats(pl, p + "mix.dkv", {A.rank + A.rot_dim, W}));
+            append(in, read_floats(pl, p + "mix.g", {A.heads * A.vdim, W}));
+            A.in = upload_matrix(e, in, A.q_rank + A.rank + A.rot_dim + A.heads * A.vdim, W);
+            A.q_up = upload_matrix(e, read_floats(pl, p + "mix.uq", {A.heads * qd, A.q_rank}).v, A.heads * qd, A.q_rank);
+            {   // per head the key up-projection [dim, rank] becomes [rank, dim]: q_abs = (W_uk^h)^T q^h as a linear with weight [out = rank, in = dim]
+                HostTensor uk = read_floats(pl, p + "mix.uk", {A.heads * A.dim, A.rank});
+                std::vector<float> t((size_t)A.heads * A.rank * std::max(A.dim, 1u));
+                for (uint32_t h = 0; h < A.heads; ++h)
+                    for (uint32_t d = 0; d < A.dim; ++d)
+                        for (uint32_t r = 0; r < A.rank; ++r) t[((size_t)h * A.rank + r) * A.dim + d] = uk.v[((size_t)h * A.dim + d) * A.rank + r];
+                t.resize((size_t)A.heads * A.rank * A.dim);
+                if (A.dim) A.key_absorb = upload_matrix(e, t, A.rank, A.dim, A.heads);
+            }
+            A.value_up = upload_matrix(e, read_floats(pl, p + "mix.uv", {A.heads * A.vdim, A.rank}).v, A.vdim, A.rank, A.heads);
+            A.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
+            A.q_norm = upload_f32(e, read_floats(pl, p + "mix.dq.norm", {A.q_rank}).v);
+            A.latent_norm = upload_f32(e, read_floats(pl, p + "mix.dkv.norm", {A.rank}).v);
+            wbytes += A.in.bytes + A.q_up.bytes + A.key_absorb.bytes + A.value_up.bytes + A.out.bytes;
+            kvb += (uint64_t)(A.rank + A.rot_dim) * storage_size(e->store_dt);
+            n_cache++;
+        } else {
+            throw std::runtime_error("layer type '" + type + "' is not known to the parallel-block family");
+        }
+        GatedMlp& M = L.gmlp;
+        const Json* ml = lc.get("mlp");
+        if (ml && !ml->is_null()) {
+            const std::string kind = ml->at("kind").str;
+            if (kind == "dense") {
+                M.kind = GatedMlp::Dense;
+                M.f = cfg_u32(*ml, "ff");
+                M.limit = (float)ml->at("limit").number();
+                std::vector<float> gu;
+                append(gu, read_floats(pl, p + "mlp.gate", {M.f, W}));
+                append(gu, read_floats(pl, p + "mlp.up", {M.f, W}));
+                M.gate_up = upload_matrix(e, gu, 2 * M.f, W);
+                M.down = upload_matrix(e, read_floats(pl, p + "mlp.down", {W, M.f}).v, W, M.f);
+                wbytes += M.gate_up.bytes + M.down.bytes;
+            } else if (kind == "moe") {
+                M.kind = GatedMlp::TableExperts;
+                const Json& ex = ml->at("expert");
+                const Json& ro = ml->at("router");
+                M.f = cfg_u32(ex, "ff");
+                M.limit = (float)ex.at("limit").number();
+                M.experts = cfg_u32(ro, "experts");
+                M.top = cfg_u32(ro, "top");
+                if (M.experts == 0 || M.top == 0 || M.top > M.experts || M.experts > 8192 || (uint64_t)MAX_ROWS * M.top * 2 > 40000) throw std::runtime_error(p + "mlp: bad expert / top counts");
+                std::vector<float> gu, dn;
+                for (uint32_t x = 0; x < M.experts; ++x) {
+                    const std::string q = p + "mlp.e" + std::to_string(x) + ".";
+                    append(gu, read_floats(pl, q + "gate", {M.f, W}));
+                    append(gu, read_floats(pl, q + "up", {M.f, W}));
+                    append(dn, read_floats(pl, q + "down", {W, M.f}));
+                }
+                M.gate_up = upload_matrix(e, gu, 2 * M.f, W, M.experts);
+                M.down = upload_matrix(e, dn, W, M.f, M.experts);
+                const TensorInfo& tt = pl.validate(p + "mlp.table", {V, M.top}, "I32");
+                M.table = make_buf(e, tt.end - tt.begin, UZU_BUFFER_MANAGED);
+                pl.read_into(tt, uzu_buffer_cpu_ptr(M.table.b));
+                check(uzu_buffer_make_resident(e->ctx, M.table.b));
+                wbytes += (M.gate_up.bytes + M.down.bytes) / M.experts * M.top;
+            } else {
+                throw std::runtime_error("mlp kind '" + kind + "' is not known to the parallel-block family");
+            }
+        }
+    }
+    pl.assert_all_validated();
+    e->info.model_dim = W;
+    e->info.hidden_dim = 0;
+    e->info.vocab_size = V;
+    e->info.num_layers = (uint32_t)e->layers.size();
+    e->info.num_attention_layers = n_cache;
+    e->info.num_delta_net_layers = n_rec;
+    e->info.weight_bytes_per_token = wbytes;
+    e->info.kv_bytes_per_token_per_ctx = kvb;
+    e->info.state_bytes_per_token = stb;
+}
+
+// scratch of the family: f32 row blocks sized by the widest layer
+static void create_parallel_block_scratch(uzu_engine* e) {
+    if (!e->parallel_block) return;
+    const uint32_t W = e->model_dim;
+    uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1;
+    for (const Layer& L : e->layers) {
+        if (L.kind == MixGeneralDelta) {
+            const uint32_t HD = L.gd.heads * L.gd.dim;
+            proj = std::max(proj, L.gd.in.rows);
+            lat = std::max(lat, L.gd.decay_rank);
+            wide = std::max(wide, HD);
+            mixed = std::max(mixed, HD);
+            gated = std::max(gated, HD);
+        } else {
+            const LatentAttentionLayer& A = L.la;
+            proj = std::max(proj, A.in.rows);
+            lat = std::max(lat, A.q_rank);
+            wide = std::max(wide, A.heads * (A.dim + A.rot_dim));
+            query = std::max(query, A.heads * (A.rank + A.rot_dim));
+            mixed = std::max(mixed, A.heads * A.rank);
+            gated = std::max(gated, A.heads * A.vdim);
+        }
+        if (L.gmlp.kind != GatedMlp::None) {
+            gu = std::max(gu, 2 * L.gmlp.f);
+            act = std::max(act, L.gmlp.f);
+            top = std::max(top, L.gmlp.top);
+            experts = std::max(experts, L.gmlp.experts);
+        }
+    }
+    auto dev = [&](size_t bytes) { return make_buf(e, std::max<size_t>(bytes, 256), UZU_BUFFER_DEVICE); };
+    const size_t R = MAX_ROWS;
+    auto& P = e->pb;
+    P.resid = dev(R * W * 4);
+    P.normed = dev(R * W * 4);
+    P.proj = dev(R * proj * 4);
+    P.lat = dev(R * lat * 4);
+    P.wide = dev(R * wide * 4);
+    P.query = dev(R * query * 4);
+    P.mixed = dev(R * mixed * 4);
+    P.gated_mix = dev(R * std::max(gated, mixed) * 4);
+    P.mix_out = dev(R * W * 4);
+    P.gate_up = dev(R * top * gu * 4);
+    P.act = dev(R * top * act * 4);
+    P.pair_out = dev(R * top * W * 4);
+    P.ff_out = dev(R * W * 4);
+    P.group_offsets = dev((size_t)(experts + 1) * 4);
+    P.rows_map = dev(R * top * 4);
+    P.pair_pos = dev(R * top * 4);
+    P.normed_rows = dev((size_t)e->logits_rows * W * 4);
+    P.logits_f32 = dev((size_t)e->logits_rows * e->vocab * 4);
+}
+
+static uzu_dense_linear_args dense_args(const uzu_engine* e, const DenseMatrix& m, uint64_t a, uint32_t rows, uint64_t d) {
+    uzu_dense_linear_args x{};
+    x.a = a; x.w = m.w.ptr(); x.d = d;
+    x.m = rows; x.n = m.rows; x.k = m.cols; x.lda = m.cols; x.ldd = m.rows; x.batch = 1;
+    x.weights_dt = e->store_dt; x.scale = 1.0f;
+    return x;
+}
+
+static void encode_dense(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatrix& m, uint64_t a, uint32_t lda, uint32_t rows, uint64_t d) {
+    uzu_dense_linear_args x = dense_args(e, m, a, rows, d);
+    x.lda = lda;
+    uzu_dense_linear_encode(cmd, &x);
+}
+
+// h [m, W] -> mixer output [m, W] in pb.mix_out
+static void encode_general_delta(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+    const GeneralDeltaLayer& G = L.gd;
+    auto& P = e->pb;
+    const uint32_t m = pc.m, HD = G.heads * G.dim, ld = G.in.rows;
+    encode_dense(e, cmd, G.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [r | k | v | rate | gate | decay latent]
+    uzu_unary_f32_encode(cmd, P.proj.ptr() + (uint64_t)5 * HD * 4, ld, P.lat.ptr(), G.decay_rank, m, G.decay_rank, 0);   // tanh
+    encode_dense(e, cmd, G.decay_up, P.lat.ptr(), G.decay_rank, m, P.wide.ptr());           // decay logits [m, HD]
+    uzu_general_delta_args ga{};
+    ga.r = P.proj.ptr(); ga.k = P.proj.ptr() + (uint64_t)HD * 4; ga.v = P.proj.ptr() + (uint64_t)2 * HD * 4;
+    ga.rate_logit = P.proj.ptr() + (uint64_t)3 * HD * 4; ga.decay_logit = P.wide.ptr();
+    ga.rate_bias = G.rate_bias.ptr(); ga.decay_bias = G.decay_bias.ptr();
+    ga.state = S.ssm_state.ptr(); ga.out = P.mixed.ptr();
+    ga.r_stride = ga.k_stride = ga.v_stride = ga.rate_stride = ld; ga.decay_stride = HD;
+    ga.rows = m; ga.heads = G.heads; ga.dim = G.dim;
+    uzu_general_delta_encode(cmd, &ga);
+    uzu_head_norm_gate_args na{};
+    na.x = P.mixed.ptr(); na.scales = G.norm_weight.ptr(); na.gate = P.proj.ptr() + (uint64_t)4 * HD * 4; na.out = P.gated_mix.ptr();
+    na.rows = m; na.heads = G.heads; na.dim = G.dim; na.x_stride = HD; na.gate_stride = ld; na.out_stride = HD; na.normalize = 1;
+    na.epsilon = e->norm_eps;
+    uzu_head_norm_gate_encode(cmd, &na);
+    encode_dense(e, cmd, G.out, P.gated_mix.ptr(), HD, m, P.mix_out.ptr());
+}
+
+static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
+    const LatentAttentionLayer& A = L.la;
+    auto& P = e->pb;
+    const uint32_t m = pc.m, ld = A.in.rows, qd = A.dim + A.rot_dim, width = A.rank + A.rot_dim;
+    const uint64_t dyn = pc.dynamic ? e->decode_state.ptr() : 0;
+    encode_dense(e, cmd, A.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [query latent | kv latent | rotated key | gate]
+    uzu_group_rms_norm_args qn{};
+    qn.input = P.proj.ptr(); qn.scales = A.q_norm.ptr(); qn.output = P.lat.ptr();
+    qn.rows = m; qn.n = A.q_rank; qn.groups = 1; qn.in_stride = ld; qn.out_stride = A.q_rank; qn.epsilon = e->norm_eps;
+    uzu_group_rms_norm_encode(cmd, &qn);
+    encode_dense(e, cmd, A.q_up, P.lat.ptr(), A.q_rank, m, P.wide.ptr());                  // q [m, heads, dim + rot_dim]
+    uzu_latent_prepare_args pa{};
+    pa.kv = P.proj.ptr() + (uint64_t)A.q_rank * 4; pa.q = P.wide.ptr(); pa.query = P.query.ptr(); pa.cache = S.keys;
+    pa.latent_scales = A.latent_norm.ptr();
+    if (A.rope_index >= 0) {
+        pa.cosines = e->rope_cos[A.rope_index].ptr(); pa.sines = e->rope_sin[A.rope_index].ptr();
+        pa.rot_pairs = e->ropes[A.rope_index].head_dim / 2;
+    }
+    pa.dynamic_position = dyn;
+    pa.rows = m; pa.heads = A.heads; pa.dim = A.dim; pa.rot_dim = A.rot_dim; pa.rank = A.rank; pa.kv_stride = ld; pa.q_stride = A.heads * qd;
+    pa.prefix = S.length; pa.cache_dt = e->store_dt; pa.epsilon = e->norm_eps;
+    uzu_latent_prepare_encode(cmd, &pa);
+    if (A.dim) {   // absorbed key projection, one z per head: query[:, h, 0:rank] = q[:, h, 0:dim] . (W_uk^h as [rank, dim])^T
+        uzu_dense_linear_args x = dense_args(e, A.key_absorb, P.wide.ptr(), m, P.query.ptr());
+        x.lda = A.heads * qd; x.ldd = A.heads * width; x.batch = A.heads;
+        x.a_z_stride = qd; x.w_z_stride = A.key_absorb.stride(); x.d_z_stride = width;
+        uzu_dense_linear_encode(cmd, &x);
+    } else {
+        cmd->record_error(UZU_ERROR_UNSUPPORTED, "latent attention without an unrotated key part is not built");
+    }
+    uzu_latent_attention_args aa{};
+    aa.query = P.query.ptr(); aa.cache = S.keys; aa.out = P.mixed.ptr(); aa.dynamic_position = dyn;
+    aa.rows = m; aa.heads = A.heads; aa.rank = A.rank; aa.rot_dim = A.rot_dim; aa.prefix = S.length; aa.cache_dt = e->store_dt; aa.scale = A.scale;
+    uzu_latent_attention_encode(cmd, &aa);
+    {   // value projection per head: o[:, h, :] = (sum_j p_j c_j) . (W_uv^h)^T
+        uzu_dense_linear_args x = dense_args(e, A.value_up, P.mixed.ptr(), m, P.gated_mix.ptr());
+        x.lda = A.heads * A.rank; x.ldd = A.heads * A.vdim; x.batch = A.heads;
+        x.a_z_stride = A.rank; x.w_z_stride = A.value_up.stride(); x.d_z_stride = A.vdim;
+        uzu_dense_linear_encode(cmd, &x);
+    }
+    uzu_head_norm_gate_args ga{};
+    ga.x = P.gated_mix.ptr(); ga.gate = P.proj.ptr() + (uint64_t)(A.q_rank + width) * 4; ga.out = P.gated_mix.ptr();
+    ga.rows = m; ga.heads = A.heads; ga.dim = A.vdim; ga.x_stride = A.heads * A.vdim; ga.gate_stride = ld; ga.out_stride = A.heads * A.vdim;
+    uzu_head_norm_gate_encode(cmd, &ga);
+    encode_dense(e, cmd, A.out, P.gated_mix.ptr(), A.heads * A.vdim, m, P.mix_out.ptr());
+}
+
+// h [m, W] -> feed-forward output [m, W] in pb.ff_out
+static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, const PassCtx& pc) {
+    const GatedMlp& M = L.gmlp;
+    auto& P = e->pb;
+    const uint32_t m = pc.m, W = e->model_dim;
+    constexpr float kGateSlope = 1.702f;
+    if (M.kind == GatedMlp::Dense) {
+        encode_dense(e, cmd, M.gate_up, P.normed.ptr(), W, m, P.gate_up.ptr());
+        uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m, M.f, M.limit, kGateSlope);
+        encode_dense(e, cmd, M.down, P.act.ptr(), M.f, m, P.ff_out.ptr());
+        return;
+    }
+    // table-routed experts: expert-sorted (token, slot) pairs, grouped products over the pairs, weighted combine per token
+    uzu_table_route_args ra{};
+    ra.token_ids = e->token_ids.ptr(); ra.table = M.table.ptr(); ra.group_offsets = P.group_offsets.ptr(); ra.rows_map = P.rows_map.ptr();
+    ra.pair_pos = P.pair_pos.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts; ra.vocab = e->vocab;
+    uzu_table_route_encode(cmd, &ra);
+    uzu_dense_linear_args up = dense_args(e, M.gate_up, P.normed.ptr(), m, P.gate_up.ptr());
+    up.lda = W; up.batch = M.experts; up.w_z_stride = M.gate_up.stride();
+    up.group_offsets = P.group_offsets.ptr(); up.rows_map = P.rows_map.ptr();
+    uzu_dense_linear_encode(cmd, &up);
+    uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m * M.top, M.f, M.limit, kGateSlope);
+    uzu_dense_linear_args dn = dense_args(e, M.down, P.act.ptr(), m, P.pair_out.ptr());
+    dn.lda = M.f; dn.batch = M.experts; dn.w_z_stride = M.down.stride();
+    dn.group_offsets = P.group_offsets.ptr();
+    uzu_dense_linear_encode(cmd, &dn);
+    uzu_routed_combine_encode(cmd, P.pair_out.ptr(), P.pair_pos.ptr(), P.ff_out.ptr(), m, M.top, W, 1.0f / (float)M.top, 0);
+}
+
+static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx& pc, uint32_t row_begin, uint32_t row_end) {
+    const uint32_t m = pc.m, W = e->model_dim;
+    auto& P = e->pb;
+    if (pc.trie) {
+        cmd->record_error(UZU_ERROR_UNSUPPORTED, "speculation passes are not built for the parallel-block family");
+        return;
+    }
+    uzu_embedding_f32_encode(cmd, e->token_ids.ptr(), e->pb_embed.w.ptr(), e->store_dt, P.resid.ptr(), m, e->vocab, W);
+    const bool dump = P.dump && !pc.dynamic && P.layer_dump.b;
+    for (size_t i = 0; i < e->layers.size(); ++i) {
+        Layer& L = e->layers[i];
+        LayerState& S = e->state[i];
+        uzu_group_rms_norm_args na{};
+        na.input = P.resid.ptr(); na.scales = L.pre_mixer.scales.ptr(); na.output = P.normed.ptr();
+        na.rows = m; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
+        uzu_group_rms_norm_encode(cmd, &na);
+        if (L.kind == MixGeneralDelta) encode_general_delta(e, cmd, L, S, pc);
+        else encode_latent_attention(e, cmd, L, S, pc);
+        const bool ff = L.gmlp.kind != GatedMlp::None;
+        if (ff) encode_gated_mlp(e, cmd, L, pc);
+        uzu_residual_add_encode(cmd, P.resid.ptr(), P.mix_out.ptr(), ff ? P.ff_out.ptr() : 0, m * W);
+        if (dump) uzu_command_buffer_encode_copy(cmd, P.resid.ptr(), P.layer_dump.ptr() + (uint64_t)i * MAX_ROWS * W * 4, (size_t)m * W * 4);
+    }
+    if (dump) P.dump_rows = m;
+    encode_parallel_block_readout(e, cmd, row_begin, row_end);
+}
+
+static void encode_parallel_block_readout(uzu_engine* e, uzu_command_buffer* cmd, uint32_t row_begin, uint32_t row_end) {
+    if (row_end <= row_begin) return;
+    const uint32_t rows = row_end - row_begin, W = e->model_dim;
+    auto& P = e->pb;
+    uzu_group_rms_norm_args na{};
+    na.input = P.resid.ptr() + (uint64_t)row_begin * W * 4; na.scales = e->pb_final_norm.ptr(); na.output = P.normed_rows.ptr();
+    na.rows = rows; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
+    uzu_group_rms_norm_encode(cmd, &na);
+    encode_dense(e, cmd, e->pb_head, P.normed_rows.ptr(), W, rows, P.logits_f32.ptr());
+    uzu_logit_cap_f32_encode(cmd, P.logits_f32.ptr(), e->logits.ptr(), rows * e->vocab, e->logit_soft_cap, e->has_logit_soft_cap);
+}
