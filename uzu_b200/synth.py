@@ -325,3 +325,118 @@ def tiny(kind="llama", quant: QuantSpec | None = None, layers=2) -> ModelSpec:
 
 
 PRESETS = {"llama3-8b": llama3_8b, "llama3-70b": llama3_70b, "qwen3.5-0.8b": qwen35_0p8b}
+
+
+# ---------------------------------------------------------------------------------------------
+# Punilix (parallel-block family): config.json {"architecture": "Punilix", "width", "vocab", "norm": {"eps", "groups"},
+# "logit_softcap", "layers": [{"type", "mixer", "mlp"}]}; tensors embed, head, final.norm, l<i>.norm1, l<i>.mix.*, l<i>.mlp.*
+# ---------------------------------------------------------------------------------------------
+def punilix_delta_layer(heads: int, dim: int, mlp: dict | None) -> dict:
+    return {"type": "general_delta", "mixer": {"heads": heads, "dim": dim}, "mlp": mlp}
+
+
+def punilix_latent_layer(heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int, mlp: dict | None, scale: float | None = None,
+                         base: float = 10000.0, scaling: dict | None = None) -> dict:
+    rot = {"base": base, "dims": rot_dim, "scaling": scaling}
+    return {"type": "latent_attention",
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank, "rot": rot,
+                      "scale": float(scale if scale is not None else (dim + rot_dim) ** -0.5)},
+            "mlp": mlp}
+
+
+def punilix_dense_mlp(ff: int, limit: float = 7.0) -> dict:
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+def punilix_moe_mlp(ff: int, experts: int, top: int, limit: float = 7.0) -> dict:
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+
+
+def punilix_config(width: int, vocab: int, layers: list, norm_groups: int = 1, eps: float = 1e-5, logit_softcap: float | None = 30.0) -> dict:
+    return {"architecture": "Punilix", "width": width, "vocab": vocab, "norm": {"eps": eps, "groups": norm_groups},
+            "logit_softcap": logit_softcap, "layers": layers}
+
+
+def punilix_tensors(config: dict, seed: int = 0, decay_rank: int = 16) -> dict:
+    """Seeded random tensors of a Punilix config: float arrays are f32 values that bf16 holds exactly, tables are int32."""
+    rng = np.random.default_rng(seed)
+    W, V = config["width"], config["vocab"]
+
+    def bf(x):
+        return st_bits_to_f32(f32_to_bf16_bits(np.asarray(x, np.float32)))
+
+    def mat(rows, cols, gain=1.0):
+        return bf(rng.standard_normal((rows, cols), dtype=np.float32) * (gain / np.sqrt(cols)))
+
+    def vec(n, mean=1.0, spread=0.1):
+        return bf(mean + spread * rng.standard_normal(n, dtype=np.float32))
+
+    t = {"embed": mat(V, W, np.sqrt(W)), "head": mat(V, W, 2.0), "final.norm": vec(W)}
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        t[p + "norm1"] = vec(W)
+        m = L["mixer"]
+        if L["type"] == "general_delta":
+            hd = m["heads"] * m["dim"]
+            for nm in ("r", "k", "v", "g", "a"):
+                t[p + "mix." + nm] = mat(hd, W)
+            t[p + "mix.a.b"] = vec(hd, 0.0, 0.5)
+            t[p + "mix.w1"] = mat(decay_rank, W)
+            t[p + "mix.w2"] = mat(hd, decay_rank, 2.0)
+            t[p + "mix.w0"] = vec(hd, -1.0, 1.5)
+            t[p + "mix.norm"] = vec(hd)
+            t[p + "mix.o"] = mat(W, hd)
+        elif L["type"] == "latent_attention":
+            H, dn, dr, dv, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            t[p + "mix.dq"] = mat(Q, W)
+            t[p + "mix.dq.norm"] = vec(Q)
+            t[p + "mix.uq"] = mat(H * (dn + dr), Q, 2.0)
+            t[p + "mix.dkv"] = mat(R + dr, W)
+            t[p + "mix.dkv.norm"] = vec(R)
+            t[p + "mix.uk"] = mat(H * dn, R, 2.0)
+            t[p + "mix.uv"] = mat(H * dv, R)
+            t[p + "mix.g"] = mat(H * dv, W)
+            t[p + "mix.o"] = mat(W, H * dv)
+        else:
+            raise ValueError(L["type"])
+        ml = L.get("mlp")
+        if ml is None:
+            continue
+        if ml["kind"] == "dense":
+            t[p + "mlp.gate"], t[p + "mlp.up"], t[p + "mlp.down"] = mat(ml["ff"], W, 2.0), mat(ml["ff"], W, 2.0), mat(W, ml["ff"])
+        else:
+            f, E, top = ml["expert"]["ff"], ml["router"]["experts"], ml["router"]["top"]
+            for x in range(E):
+                q = f"{p}mlp.e{x}."
+                t[q + "gate"], t[q + "up"], t[q + "down"] = mat(f, W, 2.0), mat(f, W, 2.0), mat(W, f)
+            t[p + "mlp.table"] = np.stack([rng.permutation(E)[:top] for _ in range(V)]).astype(np.int32)
+    return t
+
+
+def write_punilix_model(config: dict, path, seed: int = 0, tensors: dict | None = None) -> Path:
+    """config.json + model.safetensors (bf16 floats, int32 tables). `tensors` overrides the seeded random ones (values are rounded to bf16)."""
+    path = Path(path)
+    path.mkdir(parents=True, exist_ok=True)
+    (path / "config.json").write_text(json.dumps(config, indent=1))
+    tensors = tensors if tensors is not None else punilix_tensors(config, seed)
+    out = {}
+    for name, v in tensors.items():
+        v = np.asarray(v)
+        out[name] = np.ascontiguousarray(v, np.int32) if np.issubdtype(v.dtype, np.integer) else st.as_bf16(f32_to_bf16_bits(v.astype(np.float32)))
+    st.save(path / "model.safetensors", out)
+    return path
+
+
+def punilix_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=0, top=2) -> dict:
+    """A layer stack of realistic sizes for benchmarks: per block one generalized-delta layer and one latent-attention layer; the
+    feed-forward is dense, or table-routed experts of the same active size when `experts` > 0."""
+    ff = ff or 4 * width
+    heads = max(width // 128, 1)
+    layers = []
+    for _ in range(blocks):
+        mlp_a = punilix_dense_mlp(ff)
+        mlp_b = punilix_moe_mlp(ff // top, experts, top) if experts else punilix_dense_mlp(ff)
+        layers.append(punilix_delta_layer(heads, 128, mlp_a))
+        layers.append(punilix_latent_layer(heads, 128, 64, 128, 512, min(1536, width), mlp_b, base=10000.0,
+                                           scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}))
+    return punilix_config(width, vocab, layers, norm_groups=1, eps=1e-6, logit_softcap=30.0)
