@@ -703,6 +703,86 @@ def run_batched(args, eng, ctx, dist, rank, world, local_rank, workload, prefill
         dist.destroy_process_group()
 
 
+# ---- model-family comparison (--family): Punilix beside the closest existing family at equal layer sizes ------------------------------
+FAMILY_SIZES = {
+    # name: (width, feed-forward, blocks of [recurrent layer, attention layer], vocab)
+    "1k": (1024, 4096, 3, 32768),
+    "2k": (2048, 8192, 3, 32768),
+    "4k": (4096, 14336, 1, 32768),
+}
+
+
+def family_models(size: str):
+    """(Punilix checkpoint, closest existing model's checkpoint) at one size: alternating recurrent / attention layers of the same
+    width, feed-forward size, head count and layer count; random weights."""
+    from uzu_b200 import synth
+    width, ff, blocks, vocab = FAMILY_SIZES[size]
+    base = Path(os.environ.get("UZU_MODEL_CACHE", "/dev/shm/uzu_b200_models"))
+    base.mkdir(parents=True, exist_ok=True)
+    pdir = base / f"punilix-{size}"
+    if not (pdir / ".done").exists():
+        synth.write_punilix_model(synth.punilix_preset(width=width, vocab=vocab, blocks=blocks, ff=ff), pdir, seed=0)
+        (pdir / ".done").write_text("ok")
+    heads = max(width // 128, 1)
+    spec = synth.ModelSpec(name=f"hybrid-{size}", model_dim=width, hidden_dim=ff, vocab_size=vocab,
+                           layer_kinds=["delta", "attn"] * blocks, num_heads=heads, num_groups=max(heads // 4, 1), head_dim=128,
+                           rope={"type": "UnscaledRoPEConfig", "base": 1e6, "max_sequence_length": 8192, "head_dim": 64},
+                           qk_norm=True, qk_norm_scale_offset=1.0, attn_gate=True, norm_eps=1e-6, norm_scale_offset=1.0, tied_embeddings=True,
+                           quant=synth.QuantSpec("int", 4, 64, False), dn_num_heads=heads, dn_num_groups=heads, dn_head_dim=128,
+                           dn_value_head_dim=128, dn_kernel_size=4)
+    qdir = base / f"hybrid-{size}"
+    if not (qdir / ".done").exists():
+        synth.write_model(spec, qdir, seed=0)
+        (qdir / ".done").write_text("ok")
+    return pdir, qdir
+
+
+def family_compare(args):
+    """One JSON line per size: prefill and decode throughput of Punilix and of the closest existing family (gated attention + DeltaNet,
+    4-bit weights) with the same layer sizes. Prefill: a prompt of --prefill tokens (default 1024) through prefill(), wall clock around
+    the synchronous call, best of 3. Decode: decode_timed (CUDA events around device-chained steps), after warm-up. Fractions are of the
+    measured peaks: decode against the bytes a token must read (weights + cache rows + states), prefill against 2 * tokens * weights."""
+    from uzu_b200 import binding as B
+    B.load()
+    hbm, hbm_src = hbm_peak()
+    tens, tens_src = tensor_peak()
+    prompt_len = args.prefill or 1024
+    steps = args.steps or 128
+    sizes = [x for x in (args.family_sizes.split(",") if args.family_sizes else ["1k", "2k"]) if x]
+    with B.Context(0) as ctx:
+        for size in sizes:
+            pdir, qdir = family_models(size)
+            line = {"family_compare": size, "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
+                                                                                                         "tensor_tflops": tens, "tensor_source": tens_src}}
+            for name, d in (("punilix", pdir), ("closest_existing", qdir)):
+                with B.Engine(ctx, d, max_context_length=prompt_len + steps + 64, use_cuda_graph=not args.no_graph) as eng:
+                    vocab = eng.info.vocab_size
+                    prompt = ((np.arange(prompt_len, dtype=np.int64) * 7919 + 13) % vocab).astype(np.uint32)
+                    best = 1e9
+                    for _ in range(4):
+                        eng.reset()
+                        t0 = time.perf_counter()
+                        eng.prefill(prompt)
+                        best = min(best, time.perf_counter() - t0)
+                    eng.snapshot()
+                    eng.decode_timed(max(args.warmup, 3))
+                    eng.restore()
+                    l0 = eng.launch_count
+                    sec = eng.decode_timed(steps)
+                    launches = (eng.launch_count - l0) / steps
+                    info = eng.info
+                    params = info.weight_bytes_per_token / (2.0 if name == "punilix" else 0.5625)      # bf16, or 4-bit codes + a bf16 scale and a 4-bit zero point per 64
+                    step_bytes = info.weight_bytes_per_token + info.kv_bytes_per_token_per_ctx * (prompt_len + steps / 2) + info.state_bytes_per_token
+                    line[name] = {
+                        "prefill_tok_s": prompt_len / best, "prefill_ms": 1e3 * best,
+                        "prefill_tensor_frac": 2.0 * prompt_len * params / best / 1e12 / tens,
+                        "decode_tok_s": steps / sec, "decode_ms_per_token": 1e3 * sec / steps, "decode_launches_per_token": launches,
+                        "decode_bytes_per_token": int(step_bytes), "decode_hbm_frac": step_bytes / (sec / steps) / 1e9 / hbm,
+                        "decode_path": "persistent kernel" if eng.persistent_decode else "per-kernel path, CUDA graph" if not args.no_graph else "per-kernel path",
+                    }
+            print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -720,7 +800,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="decode this many independent sequences together (<= 16), one weight pass per step")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size: shard ONE model over this many ranks (= --gpus) instead of replicas")
+    ap.add_argument("--family", choices=["punilix"], default=None,
+                    help="instead of the headline workload: prefill / decode throughput of this model family beside the closest existing one at equal layer sizes (1 GPU)")
+    ap.add_argument("--family-sizes", default="", help="comma list of " + ", ".join(sorted(FAMILY_SIZES)) + " (default 1k,2k)")
     args = ap.parse_args()
+    if args.family:
+        family_compare(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

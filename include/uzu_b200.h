@@ -549,9 +549,10 @@ UZU_API void uzu_latent_prepare_encode(uzu_command_buffer* cmd, const uzu_latent
  * cache[j,:] for j <= prefix + t, out[t, h, :] = sum_j softmax_j * cache[j, 0:rank]  (f32 [rows, heads, rank]). */
 typedef struct uzu_latent_attention_args {
     uint64_t query, cache, out, dynamic_position;
+    uint64_t partials;             /* scratch f32 [rows, heads, splits, rank + 2] when splits > 1 */
     uint32_t rows, heads, rank, rot_dim, prefix, cache_dt;
     float scale;
-    uint32_t reserved;
+    uint32_t splits;               /* the causal key range of every query is cut into this many parts, one CTA each (0 / 1 = none) */
 } uzu_latent_attention_args;
 UZU_API void uzu_latent_attention_encode(uzu_command_buffer* cmd, const uzu_latent_attention_args* args);
 

@@ -89,6 +89,17 @@ def test_dense_linear_plain(ctx, m, f32_weights):
     close(got, (t64(a) @ t64(w).T).numpy(), 3e-6, "dense linear")
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 40, 2048), (5, 40, 2048), (3, 2100, 1024), (2, 9, 1100), (8, 13, 4100)])
+@pytest.mark.parametrize("f32_weights", [True, False])
+def test_dense_linear_long_rows_shared_by_warps(ctx, m, n, k, f32_weights):
+    """Few output features with a long k: several warps take slices of one weight row (also a k that is no multiple of a vector load)."""
+    rng = np.random.default_rng(n + k)
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    w = synth.st_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32)))
+    got = dense_linear(ctx, a, w[None], f32_weights=f32_weights, d=np.zeros((m, n), np.float32))
+    close(got, (t64(a) @ t64(w).T).numpy(), 3e-6, "dense linear, sliced k")
+
+
 @pytest.mark.parametrize("m", [2, 40])
 def test_dense_linear_heads_and_accumulate(ctx, m):
     """z-batches: head z reads its own column block of A and its own weight and writes its own column block of D."""
@@ -232,7 +243,7 @@ def rope_tables(rot, positions):
     return (torch.cos(ang) * mult).to(torch.float32).numpy(), (torch.sin(ang) * mult).to(torch.float32).numpy()
 
 
-def latent_gpu(ctx, q, kv, uk, norm_w, m, eps, prefix, cache, f32_cache=True):
+def latent_gpu(ctx, q, kv, uk, norm_w, m, eps, prefix, cache, f32_cache=True, splits=0):
     """q [T, H, dim + rot], kv [T, rank + rot] raw projections; cache [capacity, rank + rot] holds the rows of earlier tokens.
     Returns the weighted latent sums [T, H, rank] and the cache."""
     T, H, dn, dr, R = q.shape[0], m["heads"], m["dim"], m["rot_dim"], m["kv_rank"]
@@ -252,8 +263,9 @@ def latent_gpu(ctx, q, kv, uk, norm_w, m, eps, prefix, cache, f32_cache=True):
     for h in range(H):
         query[:, h, :R] = (q[:, h, :dn].astype(np.float64) @ uk[h].astype(np.float64)).astype(np.float32)
     bquery2 = ctx.upload(query)
-    aa = B.LatentAttentionArgs(query=bquery2.ptr, cache=bcache.ptr, out=bout.ptr, rows=T, heads=H, rank=R, rot_dim=dr, prefix=prefix, cache_dt=dt,
-                               scale=m["scale"])
+    bpart = ctx.upload(np.zeros(T * H * max(splits, 1) * (R + 2), np.float32))
+    aa = B.LatentAttentionArgs(query=bquery2.ptr, cache=bcache.ptr, out=bout.ptr, partials=bpart.ptr, rows=T, heads=H, rank=R, rot_dim=dr,
+                               prefix=prefix, cache_dt=dt, scale=m["scale"], splits=splits)
     run(ctx, "uzu_latent_attention_encode", C.byref(aa))
     new_cache = bcache.numpy(np.float32, cache.shape) if f32_cache else synth.st_bits_to_f32(bcache.numpy(np.uint16, cache.shape))
     return bout.numpy(np.float32, (T, H, R)), new_cache
@@ -292,6 +304,7 @@ YARN = {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}
     (9, 31, 11, 16, 8, 24, 6, YARN),          # more heads than one CTA's group, rotation of a part of the rotated block, tile edge at 32 keys
     (33, 64, 2, 20, 16, 70, None, YARN),
     (1, 200, 9, 8, 32, 130, None, None),      # one decoded token far into the context
+    (2, 300, 3, 8, 5, 20, 4, None),           # an odd row width: the tile is staged element by element
 ])
 def test_latent_attention_kernels(ctx, T, prefix, heads, dim, rot, rank, dims, scaling):
     rng = np.random.default_rng(T + prefix)
@@ -303,10 +316,11 @@ def test_latent_attention_kernels(ctx, T, prefix, heads, dim, rot, rank, dims, s
     cache = np.zeros((prefix + T + 3, rank + rot), np.float32)
     cache[:prefix] = rng.standard_normal((prefix, rank + rot), dtype=np.float32)
     cache[prefix + T:] = 1e4                    # rows beyond the causal bound must not be read
-    got, got_cache = latent_gpu(ctx, q, kv, uk, norm_w, m, 1e-5, prefix, cache)
     ref, ref_rows = latent_plain(q, kv, uk, norm_w, m, 1e-5, prefix, cache)
-    close(got_cache[:prefix + T], ref_rows, 3e-6, "cache rows")
-    close(got, ref, 2e-5, "latent attention")
+    for splits in (0, 2, 5, 64):             # key ranges cut over several CTAs and merged: also more splits than tiles (empty parts)
+        got, got_cache = latent_gpu(ctx, q, kv, uk, norm_w, m, 1e-5, prefix, cache.copy(), splits=splits)
+        close(got_cache[:prefix + T], ref_rows, 3e-6, "cache rows")
+        close(got, ref, 2e-5, f"latent attention, {splits} splits")
 
 
 @pytest.mark.parametrize("far", [0, 1, 31, 32, 33, 500])
@@ -327,7 +341,7 @@ def test_latent_attention_finds_one_far_key(ctx, far, f32_cache):
         q[:, :, 0] = 40.0
         kv = 0.05 * rng.standard_normal((T, rank + rot), dtype=np.float32)
         kv[:, 5] = 0.0                                   # the new rows' own latents do not answer the query
-        got, _ = latent_gpu(ctx, q, kv, uk, np.ones(rank, np.float32), m, 1e-5, n, cache.copy(), f32_cache)
+        got, _ = latent_gpu(ctx, q, kv, uk, np.ones(rank, np.float32), m, 1e-5, n, cache.copy(), f32_cache, splits=7 if T == 1 else 0)
         want = np.zeros(rank); want[5] = 3.0
         for t in range(T):
             for h in range(heads):

@@ -163,8 +163,8 @@ LatentPrepareArgs = _struct("uzu_latent_prepare_args", [
     ("q_stride", u32), ("prefix", u32), ("cache_dt", u32), ("epsilon", f32), ("reserved", u32)])
 
 LatentAttentionArgs = _struct("uzu_latent_attention_args", [
-    ("query", u64), ("cache", u64), ("out", u64), ("dynamic_position", u64),
-    ("rows", u32), ("heads", u32), ("rank", u32), ("rot_dim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32), ("reserved", u32)])
+    ("query", u64), ("cache", u64), ("out", u64), ("dynamic_position", u64), ("partials", u64),
+    ("rows", u32), ("heads", u32), ("rank", u32), ("rot_dim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32), ("splits", u32)])
 
 MAIN_SLOT = 0xFFFFFFFF
 

@@ -43,24 +43,30 @@ __device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, floa
 // ---- rows kernel ------------------------------------------------------------------------------------------------------------------
 constexpr int DL_MAX_ROWS = 8;
 
-template <typename TW>
+// KS warps share one output feature, each a contiguous slice of k; their partial sums meet in shared memory in slice order. Few output
+// features with a long k (a down projection) would otherwise leave most of the memory system idle.
+template <typename TW, int KS>
 __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_args a) {
+    __shared__ float part[8][DL_MAX_ROWS];
     const uint32_t z = blockIdx.y;
     const int lane = threadIdx.x & 31;
-    const uint32_t col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t warp = threadIdx.x >> 5, slice = warp % KS;
+    const uint32_t col = blockIdx.x * (8 / KS) + warp / KS;
+    const bool col_ok = col < a.n;
     pdl_launch_dependents();
-    if (col >= a.n) return;
-    const TW* w = reinterpret_cast<const TW*>(a.w) + (size_t)z * a.w_z_stride + (size_t)col * a.k;
+    const TW* w = reinterpret_cast<const TW*>(a.w) + (size_t)z * a.w_z_stride + (size_t)(col_ok ? col : 0) * a.k;
     constexpr int VEC = 16 / (int)sizeof(TW);            // weights per 128-bit load
     const bool vec_ok = (a.k % VEC == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (a.lda % 4 == 0) && ((a.a & 15) == 0) &&
-                        (a.a_z_stride % 4 == 0);
+                        (a.a_z_stride % 4 == 0) && (((size_t)a.w_z_stride * sizeof(TW)) % 16 == 0) && (((size_t)a.k * sizeof(TW)) % 16 == 0);
+    const uint32_t sweep = vec_ok ? 32 * VEC : 32;       // k covered by one pass of the warp's lanes
+    const uint32_t sweeps = (a.k + sweep - 1) / sweep, per = (sweeps + KS - 1) / KS;
+    const uint32_t k_lo = min(a.k, slice * per * sweep), k_hi = min(a.k, (slice + 1) * per * sweep);
     // the weight row does not depend on the previous kernel: with programmatic dependent launch its first loads overlap that kernel's tail
     uint4 first = make_uint4(0, 0, 0, 0);
-    const bool have_first = vec_ok && (uint32_t)lane * VEC < a.k;
-    if (have_first) first = ldg_stream_u4(w + (size_t)lane * VEC);
+    if (vec_ok && col_ok && k_lo + (uint32_t)lane * VEC < k_hi) first = ldg_stream_u4(w + k_lo + lane * VEC);
     pdl_wait();
     const DenseRows R = dense_rows(a, z);
-    if (R.count == 0) return;
+    if (R.count == 0) return;                            // uniform over the CTA
     const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
     const float* arow[DL_MAX_ROWS];
 #pragma unroll
@@ -71,36 +77,51 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     float acc[DL_MAX_ROWS];
 #pragma unroll
     for (int r = 0; r < DL_MAX_ROWS; ++r) acc[r] = 0.0f;
-    if (vec_ok) {
-        for (uint32_t k0 = lane * VEC; k0 < a.k; k0 += 32 * VEC) {
-            const uint4 raw = (k0 == (uint32_t)lane * VEC) ? first : ldg_stream_u4(w + k0);
-            float wf[VEC];
-            if constexpr (sizeof(TW) == 2) {
-                const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+    if (!col_ok) {
+        // nothing to sum; the warp still meets the others at the barrier below
+    } else if (vec_ok) {
+        // four 128-bit weight loads of a lane are in flight before the first is used
+        constexpr uint32_t STEP = 32 * VEC, BATCH = 4;
+        const uint32_t k_first = k_lo + (uint32_t)lane * VEC;
+        for (uint32_t kb = k_first; kb < k_hi; kb += BATCH * STEP) {
+            uint4 raw[BATCH];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    wf[2 * i] = __uint_as_float(u[i] << 16);
-                    wf[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
-                }
-            } else {
-                wf[0] = __uint_as_float(raw.x); wf[1] = __uint_as_float(raw.y); wf[2] = __uint_as_float(raw.z); wf[3] = __uint_as_float(raw.w);
+            for (uint32_t u = 0; u < BATCH; ++u) {
+                const uint32_t k0 = kb + u * STEP;
+                if (k0 < k_hi) raw[u] = (u == 0 && kb == k_first) ? first : ldg_stream_u4(w + k0);
             }
 #pragma unroll
-            for (int r = 0; r < DL_MAX_ROWS; ++r) {
-                if ((uint32_t)r < R.count) {
+            for (uint32_t u = 0; u < BATCH; ++u) {
+                const uint32_t k0 = kb + u * STEP;
+                if (k0 >= k_hi) break;
+                float wf[VEC];
+                if constexpr (sizeof(TW) == 2) {
+                    const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
 #pragma unroll
-                    for (int i = 0; i < VEC; i += 4) {
-                        const float4 x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
-                        acc[r] = fmaf(x.x, wf[i], acc[r]);
-                        acc[r] = fmaf(x.y, wf[i + 1], acc[r]);
-                        acc[r] = fmaf(x.z, wf[i + 2], acc[r]);
-                        acc[r] = fmaf(x.w, wf[i + 3], acc[r]);
+                    for (int i = 0; i < 4; ++i) {
+                        wf[2 * i] = __uint_as_float(w4[i] << 16);
+                        wf[2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+                    }
+                } else {
+                    wf[0] = __uint_as_float(raw[u].x); wf[1] = __uint_as_float(raw[u].y); wf[2] = __uint_as_float(raw[u].z); wf[3] = __uint_as_float(raw[u].w);
+                }
+#pragma unroll
+                for (int r = 0; r < DL_MAX_ROWS; ++r) {
+                    if ((uint32_t)r < R.count) {
+#pragma unroll
+                        for (int i = 0; i < VEC; i += 4) {
+                            const float4 x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
+                            acc[r] = fmaf(x.x, wf[i], acc[r]);
+                            acc[r] = fmaf(x.y, wf[i + 1], acc[r]);
+                            acc[r] = fmaf(x.z, wf[i + 2], acc[r]);
+                            acc[r] = fmaf(x.w, wf[i + 3], acc[r]);
+                        }
                     }
                 }
             }
         }
     } else {
-        for (uint32_t k0 = lane; k0 < a.k; k0 += 32) {
+        for (uint32_t k0 = k_lo + lane; k0 < k_hi; k0 += 32) {
             const float wv = w_to_f32<TW>(w[k0]);
 #pragma unroll
             for (int r = 0; r < DL_MAX_ROWS; ++r)
@@ -112,9 +133,21 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
         if ((uint32_t)r < R.count) {          // uniform over the warp
             const float s = warp_sum(acc[r]);
             if (lane == 0) {
-                float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col;
-                dense_store(a, d, z, col, s);
+                if constexpr (KS == 1) {
+                    if (col_ok) dense_store(a, reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col, z, col, s);
+                } else {
+                    part[warp][r] = s;
+                }
             }
+        }
+    }
+    if constexpr (KS > 1) {
+        __syncthreads();
+        if (slice == 0 && col_ok && (uint32_t)lane < R.count) {     // lane = activation row; slices added in order
+            float s = 0.0f;
+#pragma unroll
+            for (int q = 0; q < KS; ++q) s += part[warp + q][lane];
+            dense_store(a, reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + lane) * a.ldd + col, z, col, s);
         }
     }
 }
@@ -313,9 +346,20 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
     const bool bf16 = a.weights_dt == UZU_DT_BF16;
     static const bool no_tensor = getenv("UZU_DENSE_NO_TENSOR") != nullptr;
     if (a.m <= DL_MAX_ROWS) {
-        dim3 grid((a.n + 7) / 8, a.batch);
-        if (bf16) launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, a);
-        else launch(cmd, "dense_rows_kernel", dense_rows_kernel<float>, grid, dim3(256), 0, a);
+        // warps per output feature: enough warps in flight to cover the memory latency when there are few features and k is long
+        const uint32_t sweep = bf16 ? 256 : 128;
+        const uint64_t features = (uint64_t)a.n * a.batch;
+        const int ks = (features >= 4096 || a.k < 2 * sweep) ? 1 : (features >= 2048 || a.k < 4 * sweep) ? 2 : 4;
+        dim3 grid((a.n * ks + 7) / 8, a.batch);
+        if (bf16) {
+            if (ks == 1) launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16, 1>, grid, dim3(256), 0, a);
+            else if (ks == 2) launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16, 2>, grid, dim3(256), 0, a);
+            else launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16, 4>, grid, dim3(256), 0, a);
+        } else {
+            if (ks == 1) launch(cmd, "dense_rows_kernel", dense_rows_kernel<float, 1>, grid, dim3(256), 0, a);
+            else if (ks == 2) launch(cmd, "dense_rows_kernel", dense_rows_kernel<float, 2>, grid, dim3(256), 0, a);
+            else launch(cmd, "dense_rows_kernel", dense_rows_kernel<float, 4>, grid, dim3(256), 0, a);
+        }
         return;
     }
     if (bf16 && a.m >= 32 && !no_tensor) {

@@ -448,7 +448,7 @@ struct uzu_engine {
     DenseMatrix pb_embed, pb_head;
     Buf pb_final_norm;
     struct PbScratch {
-        Buf resid, normed, proj, lat, wide, query, mixed, gated_mix, mix_out, gate_up, act, pair_out, ff_out, group_offsets, rows_map, pair_pos,
+        Buf resid, normed, proj, lat, wide, query, attn_partial, mixed, gated_mix, mix_out, gate_up, act, pair_out, ff_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;
         bool dump = false;
@@ -1343,6 +1343,8 @@ static void encode_readout_tail(uzu_engine* e, uzu_command_buffer* cmd, uint32_t
     if (e->has_logit_scale || e->has_logit_soft_cap)
         uzu_logit_transform_encode(cmd, e->logits.ptr(), rows * e->vocab, e->has_logit_scale ? e->logit_scale : 1.0f, e->logit_soft_cap, e->has_logit_soft_cap);
 }
+
+static uint32_t attention_bucket(uint32_t seq);
 
 #include "engine_parallel_block.inl"
 

@@ -253,11 +253,13 @@ static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std:
     e->info.state_bytes_per_token = stb;
 }
 
+constexpr uint32_t kSplitRows = 256;   // query rows x key splits of one latent-attention launch that leaves partial softmax states
+
 // scratch of the family: f32 row blocks sized by the widest layer
 static void create_parallel_block_scratch(uzu_engine* e) {
     if (!e->parallel_block) return;
     const uint32_t W = e->model_dim;
-    uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1;
+    uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1;
     for (const Layer& L : e->layers) {
         if (L.kind == MixGeneralDelta) {
             const uint32_t HD = L.gd.heads * L.gd.dim;
@@ -274,6 +276,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             query = std::max(query, A.heads * (A.rank + A.rot_dim));
             mixed = std::max(mixed, A.heads * A.rank);
             gated = std::max(gated, A.heads * A.vdim);
+            partial = std::max(partial, A.heads * (A.rank + 2));
         }
         if (L.gmlp.kind != GatedMlp::None) {
             gu = std::max(gu, 2 * L.gmlp.f);
@@ -291,6 +294,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     P.lat = dev(R * lat * 4);
     P.wide = dev(R * wide * 4);
     P.query = dev(R * query * 4);
+    P.attn_partial = dev((size_t)kSplitRows * partial * 4);
     P.mixed = dev(R * mixed * 4);
     P.gated_mix = dev(R * std::max(gated, mixed) * 4);
     P.mix_out = dev(R * W * 4);
@@ -376,6 +380,15 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
     uzu_latent_attention_args aa{};
     aa.query = P.query.ptr(); aa.cache = S.keys; aa.out = P.mixed.ptr(); aa.dynamic_position = dyn;
     aa.rows = m; aa.heads = A.heads; aa.rank = A.rank; aa.rot_dim = A.rot_dim; aa.prefix = S.length; aa.cache_dt = e->store_dt; aa.scale = A.scale;
+    {   // few query rows (decode, short portions): cut the keys so that about two CTAs per SM run. A captured step sizes the cut for the
+        // largest context its graph serves (the graph is captured again when the context outgrows that).
+        const uint32_t bound = pc.dynamic ? attention_bucket(S.length + m) : S.length + m;
+        const uint32_t tiles = (bound + 31) / 32, groups = (A.heads + 7) / 8;
+        const uint32_t want = std::max(1u, 2u * (uint32_t)e->ctx->sm_count / std::max(1u, m * groups));
+        aa.splits = std::min({tiles, want, kSplitRows / std::max(1u, m), 64u});
+        aa.partials = P.attn_partial.ptr();
+        if (aa.splits < 2 || m > kSplitRows) aa.splits = 1;
+    }
     uzu_latent_attention_encode(cmd, &aa);
     {   // value projection per head: o[:, h, :] = (sum_j p_j c_j) . (W_uv^h)^T
         uzu_dense_linear_args x = dense_args(e, A.value_up, P.mixed.ptr(), m, P.gated_mix.ptr());

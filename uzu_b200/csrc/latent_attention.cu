@@ -3,9 +3,11 @@
 // and applied after the weighted sum (value projection), both as z-batched dense linears outside these kernels.
 //   prepare: per token the cache row (RMS norm of the latent, interleaved-pair rotation of the shared key part) and the rotated part of
 //            every head's query;
-//   attend:  one CTA per (query token, group of 8 heads): a tile of 32 cache rows is staged once in shared memory as f32 and used by
-//            all heads of the group (warp = head, lane = key for the scores, lane = latent channel for the weighted sum); running
-//            maximum / normaliser / accumulator in f32 registers (online softmax), causal bound = the query's own position.
+//   attend:  one CTA per (query token, group of 8 heads, split of the keys): a tile of 32 cache rows is staged once in shared memory as
+//            f32 and used by all heads of the group (warp = head, lane = key for the scores, lane = latent channel for the weighted
+//            sum); running maximum / normaliser / accumulator in f32 registers (online softmax), causal bound = the query's own
+//            position. A pass of few query rows (decode) splits the keys over many CTAs and a second kernel merges the partial
+//            softmax states; a prompt's rows fill the GPU by themselves and write their output directly.
 // The cache holds bf16 or f32 rows; scores, weights and sums are f32.
 #include "common.cuh"
 
@@ -67,45 +69,86 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const uzu_latent_pr
 
 constexpr int LA_HEADS = 8, LA_KEYS = 32;
 
+// words of 4 bytes: one f32 element or two bf16 elements
+__device__ __forceinline__ void word_to_f32(const float* p, float* dst) { dst[0] = *p; }
+__device__ __forceinline__ void word_to_f32(const __nv_bfloat16* p, float* dst) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(p);
+    dst[0] = __uint_as_float(u << 16);
+    dst[1] = __uint_as_float(u & 0xffff0000u);
+}
+
+// grid (query rows, head groups, key splits). Split s of a query covers the key tiles [s * per, (s + 1) * per) of its causal range; with
+// more than one split every CTA leaves (max, normaliser, unnormalised sum) in `partials` and latent_combine_kernel merges them.
 template <typename T, int RV>
 __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const uzu_latent_attention_args a) {
     extern __shared__ float la_smem[];
-    const uint32_t t = blockIdx.x, h0 = blockIdx.y * LA_HEADS;
-    const uint32_t width = a.rank + a.rot_dim, ld = width + 1;
+    const uint32_t t = blockIdx.x, h0 = blockIdx.y * LA_HEADS, split = blockIdx.z, splits = gridDim.z;
+    const uint32_t width = a.rank + a.rot_dim;
     float* qs = la_smem;                       // [LA_HEADS][width]
-    float* tile = qs + LA_HEADS * width;       // [LA_KEYS][ld]
+    float* tile = qs + LA_HEADS * width + ((4 - (LA_HEADS * width) % 4) % 4);   // [LA_KEYS][width], 16-byte aligned
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
     const uint32_t keys = prefix + t + 1;      // causal: positions 0 .. own
+    const uint32_t tiles = (keys + LA_KEYS - 1) / LA_KEYS, per = (tiles + splits - 1) / splits;
+    const uint32_t j_begin = min(keys, split * per * LA_KEYS), j_end = min(keys, (split + 1) * per * LA_KEYS);
     const uint32_t head = h0 + warp;
     const bool head_ok = head < a.heads;
     const float* q = reinterpret_cast<const float*>(a.query) + ((size_t)t * a.heads + h0) * width;
     const uint32_t group_heads = min((uint32_t)LA_HEADS, a.heads - h0);
     for (uint32_t i = tid; i < group_heads * width; i += blockDim.x) qs[i] = q[i];
     const T* cache = reinterpret_cast<const T*>(a.cache);
+    // the rows of a tile are contiguous in the cache: one flat copy in 16-byte pieces when the tile's first byte is 16-byte aligned
+    constexpr uint32_t EPV = 16 / sizeof(T);   // elements per piece
+    const bool vec_ok = ((a.cache & 15) == 0) && (((size_t)LA_KEYS * width * sizeof(T)) % 16 == 0);
     float m = -INFINITY, l = 0.0f, acc[RV];
 #pragma unroll
     for (int i = 0; i < RV; ++i) acc[i] = 0.0f;
     const float* myq = qs + warp * width;
-    for (uint32_t j0 = 0; j0 < keys; j0 += LA_KEYS) {
-        const uint32_t n = min((uint32_t)LA_KEYS, keys - j0);
+    for (uint32_t j0 = j_begin; j0 < j_end; j0 += LA_KEYS) {
+        const uint32_t n = min((uint32_t)LA_KEYS, j_end - j0);
         __syncthreads();   // the previous tile is consumed (and, the first time, the queries are staged)
-        for (uint32_t i = tid; i < n * width; i += blockDim.x) {
-            const uint32_t r = i / width, c = i % width;
-            tile[r * ld + c] = cache_load(cache + (size_t)(j0 + r) * width + c);
+        const T* src = cache + (size_t)j0 * width;
+        const uint32_t total = n * width, pieces = vec_ok ? total / EPV : 0;
+        for (uint32_t v0 = tid; v0 < pieces; v0 += 4 * blockDim.x) {      // four pieces of a thread in flight
+            uint4 raw[4];
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t v = v0 + u * blockDim.x;
+                if (v < pieces) raw[u] = *reinterpret_cast<const uint4*>(src + (size_t)v * EPV);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t v = v0 + u * blockDim.x;
+                if (v >= pieces) break;
+                float* dst = tile + (size_t)v * EPV;
+                if constexpr (sizeof(T) == 2) {
+                    *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(raw[u].x << 16), __uint_as_float(raw[u].x & 0xffff0000u),
+                                                                  __uint_as_float(raw[u].y << 16), __uint_as_float(raw[u].y & 0xffff0000u));
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(__uint_as_float(raw[u].z << 16), __uint_as_float(raw[u].z & 0xffff0000u),
+                                                                      __uint_as_float(raw[u].w << 16), __uint_as_float(raw[u].w & 0xffff0000u));
+                } else {
+                    *reinterpret_cast<uint4*>(dst) = raw[u];
+                }
+            }
         }
+        for (uint32_t i = pieces * EPV + tid; i < total; i += blockDim.x) tile[i] = cache_load(src + i);
         __syncthreads();
         if (!head_ok) continue;
         float s = -INFINITY;
         if (lane < n) {
-            const float* kr = tile + lane * ld;
+            // lane = key. Rows are `width` apart, so the lanes start `lane` channels into the dot product and wrap around: in every step
+            // the 32 lanes read 32 consecutive query entries and one entry each of 32 rows, in different banks (width even).
+            const float* kr = tile + lane * width;
             float d0 = 0.0f, d1 = 0.0f;
-            uint32_t c = 0;
-            for (; c + 1 < width; c += 2) {
+            uint32_t c = lane < width ? lane : lane % width;
+            uint32_t i = 0;
+            for (; i + 1 < width; i += 2) {
                 d0 = fmaf(myq[c], kr[c], d0);
-                d1 = fmaf(myq[c + 1], kr[c + 1], d1);
+                c = c + 1 == width ? 0 : c + 1;
+                d1 = fmaf(myq[c], kr[c], d1);
+                c = c + 1 == width ? 0 : c + 1;
             }
-            if (c < width) d0 = fmaf(myq[c], kr[c], d0);
+            if (i < width) d0 = fmaf(myq[c], kr[c], d0);
             s = (d0 + d1) * a.scale;
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -117,7 +160,7 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
         for (int i = 0; i < RV; ++i) acc[i] *= corr;
         for (uint32_t k = 0; k < n; ++k) {
             const float pk = __shfl_sync(0xffffffffu, p, k);
-            const float* vr = tile + k * ld;
+            const float* vr = tile + k * width;
 #pragma unroll
             for (int i = 0; i < RV; ++i) {
                 const uint32_t c = lane + 32 * i;
@@ -126,24 +169,78 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
         }
     }
     if (!head_ok) return;
-    float* out = reinterpret_cast<float*>(a.out) + ((size_t)t * a.heads + head) * a.rank;
-    const float inv = 1.0f / l;
+    if (splits == 1) {
+        float* out = reinterpret_cast<float*>(a.out) + ((size_t)t * a.heads + head) * a.rank;
+        const float inv = 1.0f / l;
+#pragma unroll
+        for (int i = 0; i < RV; ++i) {
+            const uint32_t c = lane + 32 * i;
+            if (c < a.rank) out[c] = acc[i] * inv;
+        }
+        return;
+    }
+    float* part = reinterpret_cast<float*>(a.partials) + (((size_t)t * a.heads + head) * splits + split) * (a.rank + 2);
+    if (lane == 0) {
+        part[0] = m;
+        part[1] = l;
+    }
 #pragma unroll
     for (int i = 0; i < RV; ++i) {
         const uint32_t c = lane + 32 * i;
-        if (c < a.rank) out[c] = acc[i] * inv;
+        if (c < a.rank) part[2 + c] = acc[i];
     }
+}
+
+// grid (query row x head, blocks of 128 channels): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s, splits taken in order.
+// splits <= 64: warp 0 forms the weights of all splits at once, then every thread sums its channel with the loads of a split batch in flight.
+__global__ void __launch_bounds__(128) latent_combine_kernel(const float* partials, float* out, uint32_t splits, uint32_t rank) {
+    __shared__ float weight[64];
+    __shared__ float inv_total;
+    const float* part = partials + (size_t)blockIdx.x * splits * (rank + 2);
+    if (threadIdx.x < 32) {
+        const uint32_t lane = threadIdx.x;
+        const float m0 = lane < splits ? part[(size_t)lane * (rank + 2)] : -INFINITY;
+        const float m1 = lane + 32 < splits ? part[(size_t)(lane + 32) * (rank + 2)] : -INFINITY;
+        const float l0 = lane < splits ? part[(size_t)lane * (rank + 2) + 1] : 0.0f;
+        const float l1 = lane + 32 < splits ? part[(size_t)(lane + 32) * (rank + 2) + 1] : 0.0f;
+        const float big = warp_max(fmaxf(m0, m1));
+        const float w0 = m0 == -INFINITY ? 0.0f : expf(m0 - big), w1 = m1 == -INFINITY ? 0.0f : expf(m1 - big);
+        weight[lane] = w0;
+        weight[lane + 32] = w1;
+        const float total = warp_sum(w0 * l0) + warp_sum(w1 * l1);
+        if (lane == 0) inv_total = 1.0f / total;
+    }
+    __syncthreads();
+    const uint32_t c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= rank) return;
+    float v = 0.0f;
+    uint32_t s = 0;
+    for (; s + 4 <= splits; s += 4) {
+        const float x0 = part[(size_t)s * (rank + 2) + 2 + c], x1 = part[(size_t)(s + 1) * (rank + 2) + 2 + c];
+        const float x2 = part[(size_t)(s + 2) * (rank + 2) + 2 + c], x3 = part[(size_t)(s + 3) * (rank + 2) + 2 + c];
+        v = fmaf(weight[s], x0, v);
+        v = fmaf(weight[s + 1], x1, v);
+        v = fmaf(weight[s + 2], x2, v);
+        v = fmaf(weight[s + 3], x3, v);
+    }
+    for (; s < splits; ++s) v = fmaf(weight[s], part[(size_t)s * (rank + 2) + 2 + c], v);
+    out[(size_t)blockIdx.x * rank + c] = v * inv_total;
 }
 
 template <typename T, int RV>
 static void launch_latent_attention(uzu_command_buffer* cmd, const uzu_latent_attention_args& a) {
     const uint32_t width = a.rank + a.rot_dim;
-    const size_t smem = ((size_t)LA_HEADS * width + (size_t)LA_KEYS * (width + 1)) * sizeof(float);
+    const size_t smem = ((size_t)LA_HEADS * width + 4 + (size_t)LA_KEYS * width) * sizeof(float);
     static std::atomic<uint64_t> done{0};
     if (smem > 48 * 1024) opt_in_dynamic_smem(cmd, latent_attention_kernel<T, RV>, (int)smem, done);
-    dim3 grid(a.rows, (a.heads + LA_HEADS - 1) / LA_HEADS);
+    const uint32_t splits = (a.splits > 1 && a.partials) ? std::min(a.splits, 64u) : 1;
+    dim3 grid(a.rows, (a.heads + LA_HEADS - 1) / LA_HEADS, splits);
     latent_attention_kernel<T, RV><<<grid, LA_HEADS * 32, smem, cmd->ctx->stream>>>(a);
     after_launch(cmd, "latent_attention_kernel");
+    if (splits > 1) {
+        latent_combine_kernel<<<dim3(a.rows * a.heads, (a.rank + 127) / 128), 128, 0, cmd->ctx->stream>>>((const float*)a.partials, (float*)a.out, splits, a.rank);
+        after_launch(cmd, "latent_combine_kernel");
+    }
 }
 
 template <typename T>
