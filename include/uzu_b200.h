@@ -468,10 +468,16 @@ typedef struct uzu_dense_linear_args {
     uint64_t group_offsets;        /* optional u32 [batch + 1] (device) */
     uint64_t rows_map;             /* optional u32 [rows] (device) */
     uint64_t a_z_stride, w_z_stride, d_z_stride;
+    uint64_t gate;                 /* optional f32 [rows, gate_ld]: the product is multiplied by sigmoid(gate[row, z*d_z_stride + col]) */
     uint32_t m, n, k, lda, ldd, batch;   /* batch = number of z (>= 1) */
     uint32_t weights_dt, accumulate;
-    float scale;                   /* applied to the product before bias / accumulation */
-    uint32_t reserved;
+    float scale;                   /* applied to the product before gate / bias / accumulation */
+    uint32_t a_op;                 /* applied to every A element as it is read: 0 none, 1 tanh */
+    uint32_t gate_ld;
+    uint32_t pair_rows;            /* m <= 8 only. Non-zero: W has a second block of rows `pair_rows` below the first; feature col forms
+                                      g = A.W[col], u = A.W[col + pair_rows] and stores the clamped gated unit
+                                      min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1) */
+    float glu_limit, glu_alpha;
 } uzu_dense_linear_args;
 UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
 

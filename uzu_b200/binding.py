@@ -133,9 +133,10 @@ FusedLinearArgs = _struct("uzu_fused_linear_args", [
 # kernels of the parallel-block family (f32 activations, dense bf16 / f32 weights)
 DenseLinearArgs = _struct("uzu_dense_linear_args", [
     ("a", u64), ("w", u64), ("d", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64),
-    ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64),
+    ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64), ("gate", u64),
     ("m", u32), ("n", u32), ("k", u32), ("lda", u32), ("ldd", u32), ("batch", u32),
-    ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("reserved", u32)])
+    ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("a_op", u32), ("gate_ld", u32), ("pair_rows", u32),
+    ("glu_limit", f32), ("glu_alpha", f32)])
 
 GroupRmsNormArgs = _struct("uzu_group_rms_norm_args", [
     ("input", u64), ("scales", u64), ("output", u64), ("row_indices", u64),

@@ -33,8 +33,12 @@ __device__ __forceinline__ float w_to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float w_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-__device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, float* d, uint32_t z, uint32_t col, float acc) {
+__device__ __forceinline__ float dense_a(const uzu_dense_linear_args& a, float x) { return a.a_op == 1 ? tanhf(x) : x; }
+
+// `row` is the compact row the value belongs to (the gate is indexed like D)
+__device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, float* d, uint32_t z, uint32_t row, uint32_t col, float acc) {
     float v = acc * a.scale;
+    if (a.gate) v *= 1.0f / (1.0f + expf(-reinterpret_cast<const float*>(a.gate)[(size_t)row * a.gate_ld + (size_t)z * a.d_z_stride + col]));
     if (a.bias && z == 0) v += reinterpret_cast<const float*>(a.bias)[col];
     if (a.accumulate) v += *d;
     *d = v;
@@ -44,10 +48,31 @@ __device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, floa
 constexpr int DL_MAX_ROWS = 8;
 
 // KS warps share one output feature, each a contiguous slice of k; their partial sums meet in shared memory in slice order. Few output
-// features with a long k (a down projection) would otherwise leave most of the memory system idle.
-template <typename TW, int KS>
+// features with a long k (a down projection) would otherwise leave most of the memory system idle. PAIR: the warp streams a second
+// weight row (`pair_rows` below the first) against the same activations and stores the clamped gated unit of the two sums.
+template <int VEC, typename TW>
+__device__ __forceinline__ void unpack_weights(const uint4& raw, float (&wf)[VEC]) {
+    if constexpr (sizeof(TW) == 2) {
+        const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            wf[2 * i] = __uint_as_float(w4[i] << 16);
+            wf[2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
+        }
+    } else {
+        wf[0] = __uint_as_float(raw.x); wf[1] = __uint_as_float(raw.y); wf[2] = __uint_as_float(raw.z); wf[3] = __uint_as_float(raw.w);
+    }
+}
+
+__device__ __forceinline__ float clamped_glu_value(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+template <typename TW, int KS, bool PAIR>
 __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_args a) {
-    __shared__ float part[8][DL_MAX_ROWS];
+    __shared__ float part[PAIR ? 2 : 1][8][DL_MAX_ROWS];
     const uint32_t z = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const uint32_t warp = threadIdx.x >> 5, slice = warp % KS;
@@ -55,6 +80,7 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     const bool col_ok = col < a.n;
     pdl_launch_dependents();
     const TW* w = reinterpret_cast<const TW*>(a.w) + (size_t)z * a.w_z_stride + (size_t)(col_ok ? col : 0) * a.k;
+    const TW* w2 = w + (size_t)(PAIR ? a.pair_rows : 0) * a.k;
     constexpr int VEC = 16 / (int)sizeof(TW);            // weights per 128-bit load
     const bool vec_ok = (a.k % VEC == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (a.lda % 4 == 0) && ((a.a & 15) == 0) &&
                         (a.a_z_stride % 4 == 0) && (((size_t)a.w_z_stride * sizeof(TW)) % 16 == 0) && (((size_t)a.k * sizeof(TW)) % 16 == 0);
@@ -74,47 +100,51 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
         const uint32_t p = R.begin + ((uint32_t)r < R.count ? r : 0);
         arow[r] = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride + (size_t)(map ? map[p] : p) * a.lda;
     }
-    float acc[DL_MAX_ROWS];
+    float acc[DL_MAX_ROWS], acc2[PAIR ? DL_MAX_ROWS : 1];
 #pragma unroll
     for (int r = 0; r < DL_MAX_ROWS; ++r) acc[r] = 0.0f;
+#pragma unroll
+    for (int r = 0; r < (PAIR ? DL_MAX_ROWS : 1); ++r) acc2[r] = 0.0f;
     if (!col_ok) {
         // nothing to sum; the warp still meets the others at the barrier below
     } else if (vec_ok) {
-        // four 128-bit weight loads of a lane are in flight before the first is used
+        // four 128-bit weight loads of a lane (eight with a second row) are in flight before the first is used
         constexpr uint32_t STEP = 32 * VEC, BATCH = 4;
         const uint32_t k_first = k_lo + (uint32_t)lane * VEC;
         for (uint32_t kb = k_first; kb < k_hi; kb += BATCH * STEP) {
-            uint4 raw[BATCH];
+            uint4 raw[BATCH], raw2[PAIR ? BATCH : 1];
 #pragma unroll
             for (uint32_t u = 0; u < BATCH; ++u) {
                 const uint32_t k0 = kb + u * STEP;
-                if (k0 < k_hi) raw[u] = (u == 0 && kb == k_first) ? first : ldg_stream_u4(w + k0);
+                if (k0 < k_hi) {
+                    raw[u] = (u == 0 && kb == k_first) ? first : ldg_stream_u4(w + k0);
+                    if constexpr (PAIR) raw2[u] = ldg_stream_u4(w2 + k0);
+                }
             }
 #pragma unroll
             for (uint32_t u = 0; u < BATCH; ++u) {
                 const uint32_t k0 = kb + u * STEP;
                 if (k0 >= k_hi) break;
-                float wf[VEC];
-                if constexpr (sizeof(TW) == 2) {
-                    const uint32_t w4[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        wf[2 * i] = __uint_as_float(w4[i] << 16);
-                        wf[2 * i + 1] = __uint_as_float(w4[i] & 0xffff0000u);
-                    }
-                } else {
-                    wf[0] = __uint_as_float(raw[u].x); wf[1] = __uint_as_float(raw[u].y); wf[2] = __uint_as_float(raw[u].z); wf[3] = __uint_as_float(raw[u].w);
-                }
+                float wf[VEC], wf2[PAIR ? VEC : 1];
+                unpack_weights<VEC, TW>(raw[u], wf);
+                if constexpr (PAIR) unpack_weights<VEC, TW>(raw2[u], wf2);
 #pragma unroll
                 for (int r = 0; r < DL_MAX_ROWS; ++r) {
                     if ((uint32_t)r < R.count) {
 #pragma unroll
                         for (int i = 0; i < VEC; i += 4) {
-                            const float4 x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
+                            float4 x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
+                            if (a.a_op) { x.x = dense_a(a, x.x); x.y = dense_a(a, x.y); x.z = dense_a(a, x.z); x.w = dense_a(a, x.w); }
                             acc[r] = fmaf(x.x, wf[i], acc[r]);
                             acc[r] = fmaf(x.y, wf[i + 1], acc[r]);
                             acc[r] = fmaf(x.z, wf[i + 2], acc[r]);
                             acc[r] = fmaf(x.w, wf[i + 3], acc[r]);
+                            if constexpr (PAIR) {
+                                acc2[r] = fmaf(x.x, wf2[i], acc2[r]);
+                                acc2[r] = fmaf(x.y, wf2[i + 1], acc2[r]);
+                                acc2[r] = fmaf(x.z, wf2[i + 2], acc2[r]);
+                                acc2[r] = fmaf(x.w, wf2[i + 3], acc2[r]);
+                            }
                         }
                     }
                 }
@@ -123,20 +153,33 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     } else {
         for (uint32_t k0 = k_lo + lane; k0 < k_hi; k0 += 32) {
             const float wv = w_to_f32<TW>(w[k0]);
+            const float wv2 = PAIR ? w_to_f32<TW>(w2[k0]) : 0.0f;
 #pragma unroll
             for (int r = 0; r < DL_MAX_ROWS; ++r)
-                if ((uint32_t)r < R.count) acc[r] = fmaf(arow[r][k0], wv, acc[r]);
+                if ((uint32_t)r < R.count) {
+                    const float x = dense_a(a, arow[r][k0]);
+                    acc[r] = fmaf(x, wv, acc[r]);
+                    if constexpr (PAIR) acc2[r] = fmaf(x, wv2, acc2[r]);
+                }
         }
     }
+    auto finish = [&](uint32_t r, float s, float s2) {
+        float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col;
+        if constexpr (PAIR) *d = clamped_glu_value(s, s2, a.glu_limit, a.glu_alpha);
+        else dense_store(a, d, z, R.begin + r, col, s);
+    };
 #pragma unroll
     for (int r = 0; r < DL_MAX_ROWS; ++r) {
         if ((uint32_t)r < R.count) {          // uniform over the warp
             const float s = warp_sum(acc[r]);
+            float s2 = 0.0f;
+            if constexpr (PAIR) s2 = warp_sum(acc2[r]);
             if (lane == 0) {
                 if constexpr (KS == 1) {
-                    if (col_ok) dense_store(a, reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col, z, col, s);
+                    if (col_ok) finish(r, s, s2);
                 } else {
-                    part[warp][r] = s;
+                    part[0][warp][r] = s;
+                    if constexpr (PAIR) part[1][warp][r] = s2;
                 }
             }
         }
@@ -144,10 +187,13 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     if constexpr (KS > 1) {
         __syncthreads();
         if (slice == 0 && col_ok && (uint32_t)lane < R.count) {     // lane = activation row; slices added in order
-            float s = 0.0f;
+            float s = 0.0f, s2 = 0.0f;
 #pragma unroll
-            for (int q = 0; q < KS; ++q) s += part[warp + q][lane];
-            dense_store(a, reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + lane) * a.ldd + col, z, col, s);
+            for (int q = 0; q < KS; ++q) {
+                s += part[0][warp + q][lane];
+                if constexpr (PAIR) s2 += part[1][warp + q][lane];
+            }
+            finish(lane, s, s2);
         }
     }
 }
@@ -183,7 +229,7 @@ __global__ void __launch_bounds__(256) dense_tile_kernel(const uzu_dense_linear_
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t k = k0 + lk + i;
-            As[lk + i][lr] = (a_ok && k < a.k) ? a_src[k] : 0.0f;
+            As[lk + i][lr] = (a_ok && k < a.k) ? dense_a(a, a_src[k]) : 0.0f;
             Ws[lk + i][lr] = (w_ok && k < a.k) ? w_to_f32<TW>(w_src[k]) : 0.0f;
         }
         __syncthreads();
@@ -208,7 +254,7 @@ __global__ void __launch_bounds__(256) dense_tile_kernel(const uzu_dense_linear_
             const uint32_t col = n0 + tx * 4 + j;
             if (col >= a.n) continue;
             float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + p) * a.ldd + col;
-            dense_store(a, d, z, col, acc[i][j]);
+            dense_store(a, d, z, R.begin + p, col, acc[i][j]);
         }
     }
 }
@@ -267,6 +313,10 @@ __global__ void __launch_bounds__(128) dense_tensor_kernel(const uzu_dense_linea
         }
     };
     auto stash = [&](int buf) {
+        if (a.a_op) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ra[i] = dense_a(a, ra[i]);
+        }
         __nv_bfloat16* as = &As[buf][sr * TC_LD + sk];
         __nv_bfloat16* ws = &Ws[buf][sr * TC_LD + sk];
 #pragma unroll
@@ -325,7 +375,7 @@ __global__ void __launch_bounds__(128) dense_tensor_kernel(const uzu_dense_linea
                 const uint32_t col = n0 + wn + j * 8 + t4 * 2 + (q & 1);
                 if (p < R.count && col < a.n) {
                     float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + p) * a.ldd + col;
-                    dense_store(a, d, z, col, acc[i][j][q]);
+                    dense_store(a, d, z, R.begin + p, col, acc[i][j][q]);
                 }
             }
 }
@@ -340,6 +390,10 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: null operand / bad dtype / bad batch");
         return;
     }
+    if (a.a_op > 1 || (a.pair_rows && (a.gate || a.bias || a.accumulate))) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: unknown A operation, or a paired epilogue combined with gate / bias / accumulate");
+        return;
+    }
     if (a.m == 0 || a.n == 0) return;
     if (a.lda == 0) a.lda = a.k;
     if (a.ldd == 0) a.ldd = a.n;
@@ -351,15 +405,21 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         const uint64_t features = (uint64_t)a.n * a.batch;
         const int ks = (features >= 4096 || a.k < 2 * sweep) ? 1 : (features >= 2048 || a.k < 4 * sweep) ? 2 : 4;
         dim3 grid((a.n * ks + 7) / 8, a.batch);
+        auto go = [&](auto kernel) { launch(cmd, "dense_rows_kernel", kernel, grid, dim3(256), 0, a); };
+        const bool pair = a.pair_rows != 0;
         if (bf16) {
-            if (ks == 1) launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16, 1>, grid, dim3(256), 0, a);
-            else if (ks == 2) launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16, 2>, grid, dim3(256), 0, a);
-            else launch(cmd, "dense_rows_kernel", dense_rows_kernel<__nv_bfloat16, 4>, grid, dim3(256), 0, a);
+            if (ks == 1) pair ? go(dense_rows_kernel<__nv_bfloat16, 1, true>) : go(dense_rows_kernel<__nv_bfloat16, 1, false>);
+            else if (ks == 2) pair ? go(dense_rows_kernel<__nv_bfloat16, 2, true>) : go(dense_rows_kernel<__nv_bfloat16, 2, false>);
+            else pair ? go(dense_rows_kernel<__nv_bfloat16, 4, true>) : go(dense_rows_kernel<__nv_bfloat16, 4, false>);
         } else {
-            if (ks == 1) launch(cmd, "dense_rows_kernel", dense_rows_kernel<float, 1>, grid, dim3(256), 0, a);
-            else if (ks == 2) launch(cmd, "dense_rows_kernel", dense_rows_kernel<float, 2>, grid, dim3(256), 0, a);
-            else launch(cmd, "dense_rows_kernel", dense_rows_kernel<float, 4>, grid, dim3(256), 0, a);
+            if (ks == 1) pair ? go(dense_rows_kernel<float, 1, true>) : go(dense_rows_kernel<float, 1, false>);
+            else if (ks == 2) pair ? go(dense_rows_kernel<float, 2, true>) : go(dense_rows_kernel<float, 2, false>);
+            else pair ? go(dense_rows_kernel<float, 4, true>) : go(dense_rows_kernel<float, 4, false>);
         }
+        return;
+    }
+    if (a.pair_rows) {
+        cmd->record_error(UZU_ERROR_UNSUPPORTED, "dense_linear: the paired gated-unit epilogue covers passes of at most 8 rows");
         return;
     }
     if (bf16 && a.m >= 32 && !no_tensor) {

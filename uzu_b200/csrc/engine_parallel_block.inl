@@ -297,11 +297,9 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     P.attn_partial = dev((size_t)kSplitRows * partial * 4);
     P.mixed = dev(R * mixed * 4);
     P.gated_mix = dev(R * std::max(gated, mixed) * 4);
-    P.mix_out = dev(R * W * 4);
     P.gate_up = dev(R * top * gu * 4);
     P.act = dev(R * top * act * 4);
     P.pair_out = dev(R * top * W * 4);
-    P.ff_out = dev(R * W * 4);
     P.group_offsets = dev((size_t)(experts + 1) * 4);
     P.rows_map = dev(R * top * 4);
     P.pair_pos = dev(R * top * 4);
@@ -323,14 +321,24 @@ static void encode_dense(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatr
     uzu_dense_linear_encode(cmd, &x);
 }
 
-// h [m, W] -> mixer output [m, W] in pb.mix_out
+// x += A . W^T: the sublayers' output projections add straight into the residual stream
+static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatrix& w, uint64_t a, uint32_t lda, uint32_t rows) {
+    uzu_dense_linear_args x = dense_args(e, w, a, rows, e->pb.resid.ptr());
+    x.lda = lda; x.accumulate = 1;
+    uzu_dense_linear_encode(cmd, &x);
+}
+
+// h [m, W] -> the mixer's output is added to the residual stream
 static void encode_general_delta(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
     const GeneralDeltaLayer& G = L.gd;
     auto& P = e->pb;
     const uint32_t m = pc.m, HD = G.heads * G.dim, ld = G.in.rows;
     encode_dense(e, cmd, G.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [r | k | v | rate | gate | decay latent]
-    uzu_unary_f32_encode(cmd, P.proj.ptr() + (uint64_t)5 * HD * 4, ld, P.lat.ptr(), G.decay_rank, m, G.decay_rank, 0);   // tanh
-    encode_dense(e, cmd, G.decay_up, P.lat.ptr(), G.decay_rank, m, P.wide.ptr());           // decay logits [m, HD]
+    {   // decay logits [m, HD] = W_up tanh(decay latent): the tanh is applied as the latent is read
+        uzu_dense_linear_args x = dense_args(e, G.decay_up, P.proj.ptr() + (uint64_t)5 * HD * 4, m, P.wide.ptr());
+        x.lda = ld; x.a_op = 1;
+        uzu_dense_linear_encode(cmd, &x);
+    }
     uzu_general_delta_args ga{};
     ga.r = P.proj.ptr(); ga.k = P.proj.ptr() + (uint64_t)HD * 4; ga.v = P.proj.ptr() + (uint64_t)2 * HD * 4;
     ga.rate_logit = P.proj.ptr() + (uint64_t)3 * HD * 4; ga.decay_logit = P.wide.ptr();
@@ -344,7 +352,7 @@ static void encode_general_delta(uzu_engine* e, uzu_command_buffer* cmd, const L
     na.rows = m; na.heads = G.heads; na.dim = G.dim; na.x_stride = HD; na.gate_stride = ld; na.out_stride = HD; na.normalize = 1;
     na.epsilon = e->norm_eps;
     uzu_head_norm_gate_encode(cmd, &na);
-    encode_dense(e, cmd, G.out, P.gated_mix.ptr(), HD, m, P.mix_out.ptr());
+    encode_into_residual(e, cmd, G.out, P.gated_mix.ptr(), HD, m);
 }
 
 static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& S, const PassCtx& pc) {
@@ -390,29 +398,35 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
         if (aa.splits < 2 || m > kSplitRows) aa.splits = 1;
     }
     uzu_latent_attention_encode(cmd, &aa);
-    {   // value projection per head: o[:, h, :] = (sum_j p_j c_j) . (W_uv^h)^T
+    {   // value projection per head, times the output gate: o[:, h, :] = (sum_j p_j c_j) . (W_uv^h)^T * sigmoid(gate[:, h, :])
         uzu_dense_linear_args x = dense_args(e, A.value_up, P.mixed.ptr(), m, P.gated_mix.ptr());
         x.lda = A.heads * A.rank; x.ldd = A.heads * A.vdim; x.batch = A.heads;
         x.a_z_stride = A.rank; x.w_z_stride = A.value_up.stride(); x.d_z_stride = A.vdim;
+        x.gate = P.proj.ptr() + (uint64_t)(A.q_rank + width) * 4; x.gate_ld = ld;
         uzu_dense_linear_encode(cmd, &x);
     }
-    uzu_head_norm_gate_args ga{};
-    ga.x = P.gated_mix.ptr(); ga.gate = P.proj.ptr() + (uint64_t)(A.q_rank + width) * 4; ga.out = P.gated_mix.ptr();
-    ga.rows = m; ga.heads = A.heads; ga.dim = A.vdim; ga.x_stride = A.heads * A.vdim; ga.gate_stride = ld; ga.out_stride = A.heads * A.vdim;
-    uzu_head_norm_gate_encode(cmd, &ga);
-    encode_dense(e, cmd, A.out, P.gated_mix.ptr(), A.heads * A.vdim, m, P.mix_out.ptr());
+    encode_into_residual(e, cmd, A.out, P.gated_mix.ptr(), A.heads * A.vdim, m);
 }
 
-// h [m, W] -> feed-forward output [m, W] in pb.ff_out
+// h [m, W] -> the feed-forward output is added to the residual stream. Passes of at most 8 rows (decode) form gate and up in one launch
+// that stores the gated unit; longer passes run the stacked [gate | up] product and the unit as two kernels.
 static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, const PassCtx& pc) {
     const GatedMlp& M = L.gmlp;
     auto& P = e->pb;
     const uint32_t m = pc.m, W = e->model_dim;
     constexpr float kGateSlope = 1.702f;
+    const bool paired = m <= 8;
+    auto gate_up_args = [&]() {
+        uzu_dense_linear_args up = dense_args(e, M.gate_up, P.normed.ptr(), m, paired ? P.act.ptr() : P.gate_up.ptr());
+        up.lda = W;
+        if (paired) { up.n = M.f; up.ldd = M.f; up.pair_rows = M.f; up.glu_limit = M.limit; up.glu_alpha = kGateSlope; }
+        return up;
+    };
     if (M.kind == GatedMlp::Dense) {
-        encode_dense(e, cmd, M.gate_up, P.normed.ptr(), W, m, P.gate_up.ptr());
-        uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m, M.f, M.limit, kGateSlope);
-        encode_dense(e, cmd, M.down, P.act.ptr(), M.f, m, P.ff_out.ptr());
+        uzu_dense_linear_args up = gate_up_args();
+        uzu_dense_linear_encode(cmd, &up);
+        if (!paired) uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m, M.f, M.limit, kGateSlope);
+        encode_into_residual(e, cmd, M.down, P.act.ptr(), M.f, m);
         return;
     }
     // table-routed experts: expert-sorted (token, slot) pairs, grouped products over the pairs, weighted combine per token
@@ -420,16 +434,16 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
     ra.token_ids = e->token_ids.ptr(); ra.table = M.table.ptr(); ra.group_offsets = P.group_offsets.ptr(); ra.rows_map = P.rows_map.ptr();
     ra.pair_pos = P.pair_pos.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts; ra.vocab = e->vocab;
     uzu_table_route_encode(cmd, &ra);
-    uzu_dense_linear_args up = dense_args(e, M.gate_up, P.normed.ptr(), m, P.gate_up.ptr());
-    up.lda = W; up.batch = M.experts; up.w_z_stride = M.gate_up.stride();
+    uzu_dense_linear_args up = gate_up_args();
+    up.batch = M.experts; up.w_z_stride = M.gate_up.stride();
     up.group_offsets = P.group_offsets.ptr(); up.rows_map = P.rows_map.ptr();
     uzu_dense_linear_encode(cmd, &up);
-    uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m * M.top, M.f, M.limit, kGateSlope);
+    if (!paired) uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m * M.top, M.f, M.limit, kGateSlope);
     uzu_dense_linear_args dn = dense_args(e, M.down, P.act.ptr(), m, P.pair_out.ptr());
     dn.lda = M.f; dn.batch = M.experts; dn.w_z_stride = M.down.stride();
     dn.group_offsets = P.group_offsets.ptr();
     uzu_dense_linear_encode(cmd, &dn);
-    uzu_routed_combine_encode(cmd, P.pair_out.ptr(), P.pair_pos.ptr(), P.ff_out.ptr(), m, M.top, W, 1.0f / (float)M.top, 0);
+    uzu_routed_combine_encode(cmd, P.pair_out.ptr(), P.pair_pos.ptr(), P.resid.ptr(), m, M.top, W, 1.0f / (float)M.top, 1);
 }
 
 static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx& pc, uint32_t row_begin, uint32_t row_end) {
@@ -450,9 +464,7 @@ static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd
         uzu_group_rms_norm_encode(cmd, &na);
         if (L.kind == MixGeneralDelta) encode_general_delta(e, cmd, L, S, pc);
         else encode_latent_attention(e, cmd, L, S, pc);
-        const bool ff = L.gmlp.kind != GatedMlp::None;
-        if (ff) encode_gated_mlp(e, cmd, L, pc);
-        uzu_residual_add_encode(cmd, P.resid.ptr(), P.mix_out.ptr(), ff ? P.ff_out.ptr() : 0, m * W);
+        if (L.gmlp.kind != GatedMlp::None) encode_gated_mlp(e, cmd, L, pc);
         if (dump) uzu_command_buffer_encode_copy(cmd, P.resid.ptr(), P.layer_dump.ptr() + (uint64_t)i * MAX_ROWS * W * 4, (size_t)m * W * 4);
     }
     if (dump) P.dump_rows = m;

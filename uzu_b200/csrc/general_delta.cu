@@ -14,6 +14,8 @@ namespace uzu {
 constexpr int GD_PART = 16;   // key channels per warp
 
 __global__ void __launch_bounds__(1024) general_delta_kernel(const uzu_general_delta_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float gd_smem[];
     const uint32_t dim = a.dim, head = blockIdx.y;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, parts = blockDim.x >> 5;
@@ -105,6 +107,8 @@ __global__ void __launch_bounds__(1024) general_delta_kernel(const uzu_general_d
 
 // one warp per (row, head)
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const uzu_head_norm_gate_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const uint32_t unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (unit >= a.rows * a.heads) return;
@@ -144,8 +148,7 @@ void uzu_general_delta_encode(uzu_command_buffer* cmd, const uzu_general_delta_a
     const size_t smem = ((size_t)2 * 5 * a->dim + (size_t)4 * parts * 32 + 64) * sizeof(float);
     static std::atomic<uint64_t> done{0};
     if (smem > 48 * 1024) opt_in_dynamic_smem(cmd, general_delta_kernel, (int)smem, done);
-    general_delta_kernel<<<dim3((a->dim + 31) / 32, a->heads), parts * 32, smem, cmd->ctx->stream>>>(*a);
-    after_launch(cmd, "general_delta_kernel");
+    launch(cmd, "general_delta_kernel", general_delta_kernel, dim3((a->dim + 31) / 32, a->heads), dim3(parts * 32), smem, *a);
 }
 
 void uzu_head_norm_gate_encode(uzu_command_buffer* cmd, const uzu_head_norm_gate_args* a) {
@@ -160,8 +163,7 @@ void uzu_head_norm_gate_encode(uzu_command_buffer* cmd, const uzu_head_norm_gate
     if (!b.gate_stride) b.gate_stride = b.heads * b.dim;
     if (!b.out_stride) b.out_stride = b.heads * b.dim;
     const uint32_t units = b.rows * b.heads;
-    head_norm_gate_kernel<<<(units + 3) / 4, 128, 0, cmd->ctx->stream>>>(b);
-    after_launch(cmd, "head_norm_gate_kernel");
+    launch(cmd, "head_norm_gate_kernel", head_norm_gate_kernel, dim3((units + 3) / 4), dim3(128), 0, b);
 }
 
 }  // extern "C"

@@ -24,14 +24,17 @@ __device__ __forceinline__ float cache_load(const __nv_bfloat16* p) { return __b
 
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(const uzu_latent_prepare_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
-    const uint32_t t = blockIdx.x;
+    const uint32_t t = blockIdx.x, unit = blockIdx.y;        // unit 0: the cache row; unit 1 + h: the rotated part of head h's query
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
     const uint32_t pos = prefix + t;
     const uint32_t width = a.rank + a.rot_dim;
     const float* cosr = reinterpret_cast<const float*>(a.cosines) + (size_t)pos * a.rot_pairs;
     const float* sinr = reinterpret_cast<const float*>(a.sines) + (size_t)pos * a.rot_pairs;
-    if (a.kv) {
+    if (unit == 0) {
+        if (!a.kv) return;
         const float* kv = reinterpret_cast<const float*>(a.kv) + (size_t)t * a.kv_stride;
         T* row = reinterpret_cast<T*>(a.cache) + (size_t)pos * width;
         const float* sc = reinterpret_cast<const float*>(a.latent_scales);
@@ -46,25 +49,18 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const uzu_latent_pr
             cache_store<T>(row + a.rank + 2 * i + 1, x1 * c + x0 * s);
         }
         for (uint32_t i = 2 * a.rot_pairs + threadIdx.x; i < a.rot_dim; i += blockDim.x) cache_store<T>(row + a.rank + i, kv[a.rank + i]);
+        return;
     }
-    if (a.q) {
-        const float* q = reinterpret_cast<const float*>(a.q) + (size_t)t * a.q_stride;
-        float* out = reinterpret_cast<float*>(a.query) + (size_t)t * a.heads * width;
-        const uint32_t per_head = a.rot_dim;
-        for (uint32_t idx = threadIdx.x; idx < a.heads * per_head; idx += blockDim.x) {
-            const uint32_t h = idx / per_head, j = idx % per_head;
-            const float* src = q + (size_t)h * (a.dim + a.rot_dim) + a.dim;
-            float v;
-            if (j < 2 * a.rot_pairs) {
-                const uint32_t i = j >> 1;
-                const float x0 = src[2 * i], x1 = src[2 * i + 1], c = cosr[i], s = sinr[i];
-                v = (j & 1) ? x1 * c + x0 * s : x0 * c - x1 * s;
-            } else {
-                v = src[j];
-            }
-            out[(size_t)h * width + a.rank + j] = v;
-        }
+    if (!a.q) return;
+    const uint32_t h = unit - 1;
+    const float* src = reinterpret_cast<const float*>(a.q) + (size_t)t * a.q_stride + (size_t)h * (a.dim + a.rot_dim) + a.dim;
+    float* out = reinterpret_cast<float*>(a.query) + ((size_t)t * a.heads + h) * width + a.rank;
+    for (uint32_t i = threadIdx.x; i < a.rot_pairs; i += blockDim.x) {
+        const float x0 = src[2 * i], x1 = src[2 * i + 1], c = cosr[i], s = sinr[i];
+        out[2 * i] = x0 * c - x1 * s;
+        out[2 * i + 1] = x1 * c + x0 * s;
     }
+    for (uint32_t i = 2 * a.rot_pairs + threadIdx.x; i < a.rot_dim; i += blockDim.x) out[i] = src[i];
 }
 
 constexpr int LA_HEADS = 8, LA_KEYS = 32;
@@ -81,6 +77,8 @@ __device__ __forceinline__ void word_to_f32(const __nv_bfloat16* p, float* dst) 
 // more than one split every CTA leaves (max, normaliser, unnormalised sum) in `partials` and latent_combine_kernel merges them.
 template <typename T, int RV>
 __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const uzu_latent_attention_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ float la_smem[];
     const uint32_t t = blockIdx.x, h0 = blockIdx.y * LA_HEADS, split = blockIdx.z, splits = gridDim.z;
     const uint32_t width = a.rank + a.rot_dim;
@@ -95,7 +93,11 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
     const bool head_ok = head < a.heads;
     const float* q = reinterpret_cast<const float*>(a.query) + ((size_t)t * a.heads + h0) * width;
     const uint32_t group_heads = min((uint32_t)LA_HEADS, a.heads - h0);
-    for (uint32_t i = tid; i < group_heads * width; i += blockDim.x) qs[i] = q[i];
+    if (width % 4 == 0 && (a.query & 15) == 0) {
+        for (uint32_t i = tid; i < group_heads * width / 4; i += blockDim.x) reinterpret_cast<float4*>(qs)[i] = reinterpret_cast<const float4*>(q)[i];
+    } else {
+        for (uint32_t i = tid; i < group_heads * width; i += blockDim.x) qs[i] = q[i];
+    }
     const T* cache = reinterpret_cast<const T*>(a.cache);
     // the rows of a tile are contiguous in the cache: one flat copy in 16-byte pieces when the tile's first byte is 16-byte aligned
     constexpr uint32_t EPV = 16 / sizeof(T);   // elements per piece
@@ -135,21 +137,35 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
         __syncthreads();
         if (!head_ok) continue;
         float s = -INFINITY;
-        if (lane < n) {
+        if (width % 4 == 0) {
+            // the warp takes the keys one after the other: every lane multiplies its 16-byte pieces of the query and of the row, the
+            // warp adds the 32 partial sums, lane k keeps the score of key k
+            const float4* q4 = reinterpret_cast<const float4*>(myq);
+            const uint32_t w4 = width / 4;
+            for (uint32_t k = 0; k < n; ++k) {
+                const float4* k4 = reinterpret_cast<const float4*>(tile + (size_t)k * width);
+                float d = 0.0f;
+                for (uint32_t c = lane; c < w4; c += 32) {
+                    const float4 x = q4[c], y = k4[c];
+                    d = fmaf(x.x, y.x, d);
+                    d = fmaf(x.y, y.y, d);
+                    d = fmaf(x.z, y.z, d);
+                    d = fmaf(x.w, y.w, d);
+                }
+                d = warp_sum(d);
+                if (lane == k) s = d * a.scale;
+            }
+        } else if (lane < n) {
             // lane = key. Rows are `width` apart, so the lanes start `lane` channels into the dot product and wrap around: in every step
-            // the 32 lanes read 32 consecutive query entries and one entry each of 32 rows, in different banks (width even).
+            // the 32 lanes read 32 consecutive query entries and one entry each of 32 rows.
             const float* kr = tile + lane * width;
-            float d0 = 0.0f, d1 = 0.0f;
-            uint32_t c = lane < width ? lane : lane % width;
-            uint32_t i = 0;
-            for (; i + 1 < width; i += 2) {
+            float d0 = 0.0f;
+            uint32_t c = lane % width;
+            for (uint32_t i = 0; i < width; ++i) {
                 d0 = fmaf(myq[c], kr[c], d0);
                 c = c + 1 == width ? 0 : c + 1;
-                d1 = fmaf(myq[c], kr[c], d1);
-                c = c + 1 == width ? 0 : c + 1;
             }
-            if (i < width) d0 = fmaf(myq[c], kr[c], d0);
-            s = (d0 + d1) * a.scale;
+            s = d0 * a.scale;
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = lane < n ? expf(s - m_new) : 0.0f;
@@ -194,6 +210,8 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
 // grid (query row x head, blocks of 128 channels): out = sum_s e^(m_s - M) acc_s / sum_s e^(m_s - M) l_s, splits taken in order.
 // splits <= 64: warp 0 forms the weights of all splits at once, then every thread sums its channel with the loads of a split batch in flight.
 __global__ void __launch_bounds__(128) latent_combine_kernel(const float* partials, float* out, uint32_t splits, uint32_t rank) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float weight[64];
     __shared__ float inv_total;
     const float* part = partials + (size_t)blockIdx.x * splits * (rank + 2);
@@ -235,11 +253,10 @@ static void launch_latent_attention(uzu_command_buffer* cmd, const uzu_latent_at
     if (smem > 48 * 1024) opt_in_dynamic_smem(cmd, latent_attention_kernel<T, RV>, (int)smem, done);
     const uint32_t splits = (a.splits > 1 && a.partials) ? std::min(a.splits, 64u) : 1;
     dim3 grid(a.rows, (a.heads + LA_HEADS - 1) / LA_HEADS, splits);
-    latent_attention_kernel<T, RV><<<grid, LA_HEADS * 32, smem, cmd->ctx->stream>>>(a);
-    after_launch(cmd, "latent_attention_kernel");
+    launch(cmd, "latent_attention_kernel", latent_attention_kernel<T, RV>, grid, dim3(LA_HEADS * 32), smem, a);
     if (splits > 1) {
-        latent_combine_kernel<<<dim3(a.rows * a.heads, (a.rank + 127) / 128), 128, 0, cmd->ctx->stream>>>((const float*)a.partials, (float*)a.out, splits, a.rank);
-        after_launch(cmd, "latent_combine_kernel");
+        launch(cmd, "latent_combine_kernel", latent_combine_kernel, dim3(a.rows * a.heads, (a.rank + 127) / 128), dim3(128), 0, (const float*)a.partials, (float*)a.out,
+               splits, a.rank);
     }
 }
 
@@ -265,9 +282,8 @@ void uzu_latent_prepare_encode(uzu_command_buffer* cmd, const uzu_latent_prepare
         return;
     }
     if (a->rows == 0) return;
-    if (a->cache_dt == UZU_DT_BF16) latent_prepare_kernel<__nv_bfloat16><<<a->rows, 128, 0, cmd->ctx->stream>>>(*a);
-    else latent_prepare_kernel<float><<<a->rows, 128, 0, cmd->ctx->stream>>>(*a);
-    after_launch(cmd, "latent_prepare_kernel");
+    if (a->cache_dt == UZU_DT_BF16) launch(cmd, "latent_prepare_kernel", latent_prepare_kernel<__nv_bfloat16>, dim3(a->rows, 1 + a->heads), dim3(128), 0, *a);
+    else launch(cmd, "latent_prepare_kernel", latent_prepare_kernel<float>, dim3(a->rows, 1 + a->heads), dim3(128), 0, *a);
 }
 
 void uzu_latent_attention_encode(uzu_command_buffer* cmd, const uzu_latent_attention_args* a) {

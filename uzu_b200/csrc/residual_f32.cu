@@ -4,33 +4,42 @@
 
 namespace uzu {
 
-// one CTA per row; each group of the row is reduced by the whole CTA in turn (groups is small)
+// one CTA per (row, group); a thread keeps up to 8 of the part's elements in registers between the sum and the scaling
 __global__ void __launch_bounds__(256) group_rms_norm_kernel(const uzu_group_rms_norm_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[32];
-    const uint32_t row = blockIdx.x;
+    const uint32_t row = blockIdx.x, g = blockIdx.y;
     const uint32_t src = a.row_indices ? reinterpret_cast<const uint32_t*>(a.row_indices)[row] : row;
-    const float* in = reinterpret_cast<const float*>(a.input) + (size_t)src * a.in_stride;
-    float* out = reinterpret_cast<float*>(a.output) + (size_t)row * a.out_stride;
-    const float* sc = reinterpret_cast<const float*>(a.scales);
-    const uint32_t part = a.n / a.groups;
-    for (uint32_t g = 0; g < a.groups; ++g) {
-        const uint32_t base = g * part;
-        float ss = 0.0f;
-        for (uint32_t i = threadIdx.x; i < part; i += blockDim.x) {
-            const float v = in[base + i];
-            ss = fmaf(v, v, ss);
-        }
-        ss = block_sum(ss, red);
-        const float inv = 1.0f / sqrtf(ss / (float)part + a.epsilon);
-        for (uint32_t i = threadIdx.x; i < part; i += blockDim.x) {
-            const float v = in[base + i] * inv;
-            out[base + i] = sc ? v * sc[base + i] : v;
-        }
+    const uint32_t part = a.n / a.groups, base = g * part;
+    const float* in = reinterpret_cast<const float*>(a.input) + (size_t)src * a.in_stride + base;
+    float* out = reinterpret_cast<float*>(a.output) + (size_t)row * a.out_stride + base;
+    const float* sc = a.scales ? reinterpret_cast<const float*>(a.scales) + base : nullptr;
+    constexpr int KEEP = 8;
+    float v[KEEP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        v[j] = i < part ? in[i] : 0.0f;
     }
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) ss = fmaf(v[j], v[j], ss);
+    for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < part; i += blockDim.x) ss = fmaf(in[i], in[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)part + a.epsilon);
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+        const uint32_t i = threadIdx.x + j * blockDim.x;
+        if (i < part) out[i] = sc ? v[j] * inv * sc[i] : v[j] * inv;
+    }
+    for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < part; i += blockDim.x) out[i] = sc ? in[i] * inv * sc[i] : in[i] * inv;
 }
 
 template <typename TW>
 __global__ void embedding_f32_kernel(const uint32_t* tokens, const TW* table, float* out, uint32_t vocab, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t row = blockIdx.y;
     const uint32_t tok = tokens[row];
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -44,6 +53,8 @@ __global__ void embedding_f32_kernel(const uint32_t* tokens, const TW* table, fl
 }
 
 __global__ void clamped_glu_kernel(const float* gate_up, float* out, uint32_t rows, uint32_t f, float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * f) return;
     const size_t r = idx / f, c = idx % f;
@@ -53,6 +64,8 @@ __global__ void clamped_glu_kernel(const float* gate_up, float* out, uint32_t ro
 }
 
 __global__ void unary_f32_kernel(const float* in, uint32_t in_stride, float* out, uint32_t out_stride, uint32_t rows, uint32_t n, uint32_t op) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * n) return;
     const size_t r = idx / n, c = idx % n;
@@ -61,6 +74,8 @@ __global__ void unary_f32_kernel(const float* in, uint32_t in_stride, float* out
 }
 
 __global__ void residual_add_kernel(float* x, const float* a, const float* b, uint32_t length) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= length) return;
     float s = a[idx];
@@ -69,6 +84,8 @@ __global__ void residual_add_kernel(float* x, const float* a, const float* b, ui
 }
 
 __global__ void logit_cap_f32_kernel(float* logits, __nv_bfloat16* copy, uint32_t length, float cap, uint32_t has_cap) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= length) return;
     float v = logits[idx];
@@ -82,6 +99,8 @@ __global__ void logit_cap_f32_kernel(float* logits, __nv_bfloat16* copy, uint32_
 // One CTA. Counting sort of the (row, slot) pairs by expert; pairs of one expert keep token order, so the lists do not depend on the
 // thread schedule. rows * top <= 1024 * top pairs; experts <= 1024.
 __global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ uint32_t counts[];   // [experts + 1]
     const uint32_t* tokens = reinterpret_cast<const uint32_t*>(a.token_ids);
     const int32_t* table = reinterpret_cast<const int32_t*>(a.table);
@@ -124,6 +143,8 @@ __global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route
 
 __global__ void routed_combine_kernel(const float* pairs, const uint32_t* pair_pos, float* out, uint32_t rows, uint32_t top, uint32_t n,
                                       float weight, uint32_t accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * n) return;
     const size_t r = idx / n, c = idx % n;
@@ -150,8 +171,7 @@ void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_rms_norm
     uzu_group_rms_norm_args b = *a;
     if (!b.in_stride) b.in_stride = b.n;
     if (!b.out_stride) b.out_stride = b.n;
-    group_rms_norm_kernel<<<b.rows, 256, 0, cmd->ctx->stream>>>(b);
-    after_launch(cmd, "group_rms_norm_kernel");
+    launch(cmd, "group_rms_norm_kernel", group_rms_norm_kernel, dim3(b.rows, b.groups), dim3(256), 0, b);
 }
 
 void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output, uint32_t rows,
@@ -159,35 +179,30 @@ void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint6
     if (!encodable(cmd, "embedding_f32") || rows == 0 || n == 0) return;
     dim3 grid(blocks256(n), rows);
     if (weights_dt == UZU_DT_BF16)
-        embedding_f32_kernel<__nv_bfloat16><<<grid, 256, 0, cmd->ctx->stream>>>((const uint32_t*)token_ids, (const __nv_bfloat16*)table, (float*)output, vocab, n);
+        launch(cmd, "embedding_f32_kernel", embedding_f32_kernel<__nv_bfloat16>, grid, dim3(256), 0, (const uint32_t*)token_ids, (const __nv_bfloat16*)table, (float*)output, vocab, n);
     else
-        embedding_f32_kernel<float><<<grid, 256, 0, cmd->ctx->stream>>>((const uint32_t*)token_ids, (const float*)table, (float*)output, vocab, n);
-    after_launch(cmd, "embedding_f32_kernel");
+        launch(cmd, "embedding_f32_kernel", embedding_f32_kernel<float>, grid, dim3(256), 0, (const uint32_t*)token_ids, (const float*)table, (float*)output, vocab, n);
 }
 
 void uzu_clamped_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f, float limit, float alpha) {
     if (!encodable(cmd, "clamped_glu") || rows == 0 || f == 0) return;
-    clamped_glu_kernel<<<blocks256((size_t)rows * f), 256, 0, cmd->ctx->stream>>>((const float*)gate_up, (float*)output, rows, f, limit, alpha);
-    after_launch(cmd, "clamped_glu_kernel");
+    launch(cmd, "clamped_glu_kernel", clamped_glu_kernel, dim3(blocks256((size_t)rows * f)), dim3(256), 0, (const float*)gate_up, (float*)output, rows, f, limit, alpha);
 }
 
 void uzu_unary_f32_encode(uzu_command_buffer* cmd, uint64_t input, uint32_t in_stride, uint64_t output, uint32_t out_stride, uint32_t rows,
                           uint32_t n, uint32_t op) {
     if (!encodable(cmd, "unary_f32") || rows == 0 || n == 0) return;
-    unary_f32_kernel<<<blocks256((size_t)rows * n), 256, 0, cmd->ctx->stream>>>((const float*)input, in_stride, (float*)output, out_stride, rows, n, op);
-    after_launch(cmd, "unary_f32_kernel");
+    launch(cmd, "unary_f32_kernel", unary_f32_kernel, dim3(blocks256((size_t)rows * n)), dim3(256), 0, (const float*)input, in_stride, (float*)output, out_stride, rows, n, op);
 }
 
 void uzu_residual_add_encode(uzu_command_buffer* cmd, uint64_t x, uint64_t a, uint64_t b, uint32_t length) {
     if (!encodable(cmd, "residual_add") || length == 0) return;
-    residual_add_kernel<<<blocks256(length), 256, 0, cmd->ctx->stream>>>((float*)x, (const float*)a, (const float*)b, length);
-    after_launch(cmd, "residual_add_kernel");
+    launch(cmd, "residual_add_kernel", residual_add_kernel, dim3(blocks256(length)), dim3(256), 0, (float*)x, (const float*)a, (const float*)b, length);
 }
 
 void uzu_logit_cap_f32_encode(uzu_command_buffer* cmd, uint64_t logits_f32, uint64_t logits_bf16, uint32_t length, float cap, uint32_t has_cap) {
     if (!encodable(cmd, "logit_cap_f32") || length == 0) return;
-    logit_cap_f32_kernel<<<blocks256(length), 256, 0, cmd->ctx->stream>>>((float*)logits_f32, (__nv_bfloat16*)logits_bf16, length, cap, has_cap);
-    after_launch(cmd, "logit_cap_f32_kernel");
+    launch(cmd, "logit_cap_f32_kernel", logit_cap_f32_kernel, dim3(blocks256(length)), dim3(256), 0, (float*)logits_f32, (__nv_bfloat16*)logits_bf16, length, cap, has_cap);
 }
 
 void uzu_table_route_encode(uzu_command_buffer* cmd, const uzu_table_route_args* a) {
@@ -202,16 +217,14 @@ void uzu_table_route_encode(uzu_command_buffer* cmd, const uzu_table_route_args*
         cmd->record_error(UZU_ERROR_UNSUPPORTED, "table_route: rows * top too large for one pass");
         return;
     }
-    table_route_kernel<<<1, 1024, smem, cmd->ctx->stream>>>(*a);
-    after_launch(cmd, "table_route_kernel");
+    launch(cmd, "table_route_kernel", table_route_kernel, dim3(1), dim3(1024), smem, *a);
 }
 
 void uzu_routed_combine_encode(uzu_command_buffer* cmd, uint64_t pairs, uint64_t pair_pos, uint64_t output, uint32_t rows, uint32_t top, uint32_t n,
                                float weight, uint32_t accumulate) {
     if (!encodable(cmd, "routed_combine") || rows == 0 || n == 0) return;
-    routed_combine_kernel<<<blocks256((size_t)rows * n), 256, 0, cmd->ctx->stream>>>((const float*)pairs, (const uint32_t*)pair_pos, (float*)output, rows,
-                                                                                   top, n, weight, accumulate);
-    after_launch(cmd, "routed_combine_kernel");
+    launch(cmd, "routed_combine_kernel", routed_combine_kernel, dim3(blocks256((size_t)rows * n)), dim3(256), 0, (const float*)pairs, (const uint32_t*)pair_pos,
+           (float*)output, rows, top, n, weight, accumulate);
 }
 
 }  // extern "C"
