@@ -70,9 +70,12 @@ __device__ __forceinline__ float clamped_glu_value(float g, float u, float limit
     return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
 }
 
+constexpr uint32_t DL_STAGE_FLOATS = 8192;   // activation rows of a group are staged in shared memory when they fit (32 KB)
+
 template <typename TW, int KS, bool PAIR>
 __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_args a) {
     __shared__ float part[PAIR ? 2 : 1][8][DL_MAX_ROWS];
+    __shared__ __align__(16) float a_s[DL_STAGE_FLOATS];
     const uint32_t z = blockIdx.y;
     const int lane = threadIdx.x & 31;
     const uint32_t warp = threadIdx.x >> 5, slice = warp % KS;
@@ -83,22 +86,50 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     const TW* w2 = w + (size_t)(PAIR ? a.pair_rows : 0) * a.k;
     constexpr int VEC = 16 / (int)sizeof(TW);            // weights per 128-bit load
     const bool vec_ok = (a.k % VEC == 0) && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && (a.lda % 4 == 0) && ((a.a & 15) == 0) &&
-                        (a.a_z_stride % 4 == 0) && (((size_t)a.w_z_stride * sizeof(TW)) % 16 == 0) && (((size_t)a.k * sizeof(TW)) % 16 == 0);
+                        (a.a_z_stride % 4 == 0) && (((size_t)a.w_z_stride * sizeof(TW)) % 16 == 0) && (((size_t)a.k * sizeof(TW)) % 16 == 0) &&
+                        (!PAIR || (((size_t)a.pair_rows * a.k * sizeof(TW)) % 16 == 0));
     const uint32_t sweep = vec_ok ? 32 * VEC : 32;       // k covered by one pass of the warp's lanes
     const uint32_t sweeps = (a.k + sweep - 1) / sweep, per = (sweeps + KS - 1) / KS;
     const uint32_t k_lo = min(a.k, slice * per * sweep), k_hi = min(a.k, (slice + 1) * per * sweep);
-    // the weight row does not depend on the previous kernel: with programmatic dependent launch its first loads overlap that kernel's tail
-    uint4 first = make_uint4(0, 0, 0, 0);
-    if (vec_ok && col_ok && k_lo + (uint32_t)lane * VEC < k_hi) first = ldg_stream_u4(w + k_lo + lane * VEC);
+    // Weight loads of a lane run two batches deep: a batch is requested before the previous one is used. The first batch does not depend
+    // on the previous kernel: with programmatic dependent launch it is in flight during that kernel's tail.
+    constexpr uint32_t STEP = 32 * VEC, BATCH = PAIR ? 2 : 4;
+    uint4 cur[BATCH], cur2[PAIR ? BATCH : 1];
+    const uint32_t k_first = k_lo + (uint32_t)lane * VEC;
+    auto request = [&](uint4 (&r)[BATCH], uint4 (&r2)[PAIR ? BATCH : 1], uint32_t kb) {
+#pragma unroll
+        for (uint32_t u = 0; u < BATCH; ++u) {
+            const uint32_t k0 = kb + u * STEP;
+            if (k0 < k_hi) {
+                r[u] = ldg_stream_u4(w + k0);
+                if constexpr (PAIR) r2[u] = ldg_stream_u4(w2 + k0);
+            }
+        }
+    };
+    if (vec_ok && col_ok) request(cur, cur2, k_first);
     pdl_wait();
     const DenseRows R = dense_rows(a, z);
     if (R.count == 0) return;                            // uniform over the CTA
     const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
+    // the group's activation rows, with the A operation applied, go to shared memory once per CTA when they fit
+    const bool staged = vec_ok && (size_t)R.count * a.k <= DL_STAGE_FLOATS;
     const float* arow[DL_MAX_ROWS];
 #pragma unroll
     for (int r = 0; r < DL_MAX_ROWS; ++r) {
         const uint32_t p = R.begin + ((uint32_t)r < R.count ? r : 0);
         arow[r] = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride + (size_t)(map ? map[p] : p) * a.lda;
+    }
+    if (staged) {
+        const uint32_t k4 = a.k / 4;
+        for (uint32_t i = threadIdx.x; i < R.count * k4; i += blockDim.x) {
+            const uint32_t r = i / k4, c = i - r * k4;
+            const uint32_t p = R.begin + r;
+            const float* src = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride + (size_t)(map ? map[p] : p) * a.lda;
+            float4 x = reinterpret_cast<const float4*>(src)[c];
+            if (a.a_op) { x.x = dense_a(a, x.x); x.y = dense_a(a, x.y); x.z = dense_a(a, x.z); x.w = dense_a(a, x.w); }
+            reinterpret_cast<float4*>(a_s)[i] = x;
+        }
+        __syncthreads();
     }
     float acc[DL_MAX_ROWS], acc2[PAIR ? DL_MAX_ROWS : 1];
 #pragma unroll
@@ -108,33 +139,28 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     if (!col_ok) {
         // nothing to sum; the warp still meets the others at the barrier below
     } else if (vec_ok) {
-        // four 128-bit weight loads of a lane (eight with a second row) are in flight before the first is used
-        constexpr uint32_t STEP = 32 * VEC, BATCH = 4;
-        const uint32_t k_first = k_lo + (uint32_t)lane * VEC;
         for (uint32_t kb = k_first; kb < k_hi; kb += BATCH * STEP) {
-            uint4 raw[BATCH], raw2[PAIR ? BATCH : 1];
-#pragma unroll
-            for (uint32_t u = 0; u < BATCH; ++u) {
-                const uint32_t k0 = kb + u * STEP;
-                if (k0 < k_hi) {
-                    raw[u] = (u == 0 && kb == k_first) ? first : ldg_stream_u4(w + k0);
-                    if constexpr (PAIR) raw2[u] = ldg_stream_u4(w2 + k0);
-                }
-            }
+            uint4 nxt[BATCH], nxt2[PAIR ? BATCH : 1];
+            if (kb + BATCH * STEP < k_hi) request(nxt, nxt2, kb + BATCH * STEP);
 #pragma unroll
             for (uint32_t u = 0; u < BATCH; ++u) {
                 const uint32_t k0 = kb + u * STEP;
                 if (k0 >= k_hi) break;
                 float wf[VEC], wf2[PAIR ? VEC : 1];
-                unpack_weights<VEC, TW>(raw[u], wf);
-                if constexpr (PAIR) unpack_weights<VEC, TW>(raw2[u], wf2);
+                unpack_weights<VEC, TW>(cur[u], wf);
+                if constexpr (PAIR) unpack_weights<VEC, TW>(cur2[u], wf2);
 #pragma unroll
                 for (int r = 0; r < DL_MAX_ROWS; ++r) {
                     if ((uint32_t)r < R.count) {
 #pragma unroll
                         for (int i = 0; i < VEC; i += 4) {
-                            float4 x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
-                            if (a.a_op) { x.x = dense_a(a, x.x); x.y = dense_a(a, x.y); x.z = dense_a(a, x.z); x.w = dense_a(a, x.w); }
+                            float4 x;
+                            if (staged) {
+                                x = *reinterpret_cast<const float4*>(a_s + (size_t)r * a.k + k0 + i);
+                            } else {
+                                x = *reinterpret_cast<const float4*>(arow[r] + k0 + i);
+                                if (a.a_op) { x.x = dense_a(a, x.x); x.y = dense_a(a, x.y); x.z = dense_a(a, x.z); x.w = dense_a(a, x.w); }
+                            }
                             acc[r] = fmaf(x.x, wf[i], acc[r]);
                             acc[r] = fmaf(x.y, wf[i + 1], acc[r]);
                             acc[r] = fmaf(x.z, wf[i + 2], acc[r]);
@@ -148,6 +174,11 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
                         }
                     }
                 }
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < BATCH; ++u) {
+                cur[u] = nxt[u];
+                if constexpr (PAIR) cur2[u] = nxt2[u];
             }
         }
     } else {
