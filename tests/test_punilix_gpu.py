@@ -76,7 +76,7 @@ def dense_linear(ctx, a, w, *, f32_weights, batch=1, a_z=0, w_z=0, d_z=0, lda=No
     return db.numpy(np.float32, d.shape)
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 31, 32, 70, 257])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 31, 32, 70, 96, 130, 257])
 @pytest.mark.parametrize("f32_weights", [True, False])
 def test_dense_linear_plain(ctx, m, f32_weights):
     rng = np.random.default_rng(m)
@@ -405,7 +405,7 @@ def tokens_for(config, n, seed=0):
 @pytest.mark.parametrize("f32", [True, False])
 def test_prompt_logits_and_layers(ctx, tmp_path, make, f32):
     pr = Pair(ctx, tmp_path, make(), seed=1, f32=f32)
-    toks = tokens_for(pr.config, 70 if f32 else 45, 1)      # bf16: 45 rows take the tensor-pipe products
+    toks = tokens_for(pr.config, 70 if f32 else 130, 1)     # bf16: 130 rows take the large-tile tensor-pipe products (50 rows elsewhere: the small tiles)
     pr.engine.debug_layer_outputs(True)
     s = pr.engine.slot_acquire()
     got = pr.engine.forward_rows(toks, list(range(len(toks))), slot=s)

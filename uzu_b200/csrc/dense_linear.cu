@@ -2,8 +2,8 @@
 // Three kernels behind one entry point (uzu_dense_linear_encode):
 //   rows kernel   (<= 8 rows per group): one warp per output feature, the weight row streamed once with 128-bit loads and multiplied
 //                 with every activation row in f32 -- the decode step's weight pass, bound by the weight bytes;
-//   tensor kernel (bf16 weights, >= 32 rows): 64 x 64 output tiles on mma.sync.m16n8k16 (bf16 x bf16 -> f32), A rounded to bf16 while
-//                 it is staged, double-buffered shared-memory tiles;
+//   tensor kernels (bf16 weights, >= 32 rows): 64 x 64 output tiles (128 x 128 with ldmatrix fragments from 96 rows on) on
+//                 mma.sync.m16n8k16 (bf16 x bf16 -> f32), A rounded to bf16 while it is staged, double-buffered shared-memory tiles;
 //   tile kernel   (everything else, and every f32-weight product of more than 8 rows): 64 x 64 tiles of f32 multiply-adds.
 // All three share the operand addressing: z-batches (per-head weights: operand z starts z*stride further in A, W and D) and row groups
 // (per-expert weights: compact rows [off[z], off[z+1]) use weight z, an optional map names the activation row a compact row reads).
@@ -411,6 +411,121 @@ __global__ void __launch_bounds__(128) dense_tensor_kernel(const uzu_dense_linea
             }
 }
 
+// ---- tensor kernel for long passes (bf16 weights, >= 96 rows): 128 x 128 tiles, 8 warps in a 2 x 4 grid, each a 64 x 32 part = 4 x 4
+// MMA tiles; fragments come from shared memory with ldmatrix (6 loads per 16 MMAs), same staging and double buffering as above.
+constexpr int T8_BM = 128, T8_BN = 128;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(256) dense_tensor128_kernel(const uzu_dense_linear_args a) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][T8_BM * TC_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][T8_BN * TC_LD];
+    const uint32_t z = blockIdx.z;
+    const DenseRows R = dense_rows(a, z);
+    const uint32_t m0 = blockIdx.y * T8_BM, n0 = blockIdx.x * T8_BN;
+    if (m0 >= R.count) return;
+    const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
+    const float* A = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride;
+    const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)z * a.w_z_stride;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, wm = (warp >> 2) * 64, wn = (warp & 3) * 32;
+    // staging: a thread owns half a row (16 k) of the A tile and of the W tile
+    const int sr = tid >> 1, sk = (tid & 1) * 16;
+    const uint32_t pa = m0 + sr;
+    const bool a_ok = pa < R.count;
+    const float* a_src = A + (size_t)(a_ok ? (map ? map[R.begin + pa] : R.begin + pa) : 0) * a.lda;
+    const bool w_ok = n0 + sr < a.n;
+    const __nv_bfloat16* w_src = W + (size_t)(w_ok ? n0 + sr : 0) * a.k;
+    const bool a_vec = (a.lda % 4 == 0) && ((a.a & 15) == 0) && (a.a_z_stride % 4 == 0) && (a.k % 4 == 0);
+    const bool w_vec = (a.k % 8 == 0) && ((a.w & 15) == 0) && (a.w_z_stride % 8 == 0);
+    float ra[16];
+    __nv_bfloat16 rw[16];
+    auto fetch = [&](uint32_t k0) {
+        const uint32_t kb = k0 + sk;
+        if (a_ok && a_vec && kb + 16 <= a.k) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 v = *reinterpret_cast<const float4*>(a_src + kb + 4 * i);
+                ra[4 * i] = v.x; ra[4 * i + 1] = v.y; ra[4 * i + 2] = v.z; ra[4 * i + 3] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ra[i] = (a_ok && kb + i < a.k) ? a_src[kb + i] : 0.0f;
+        }
+        if (w_ok && w_vec && kb + 16 <= a.k) {
+            *reinterpret_cast<uint4*>(&rw[0]) = *reinterpret_cast<const uint4*>(w_src + kb);
+            *reinterpret_cast<uint4*>(&rw[8]) = *reinterpret_cast<const uint4*>(w_src + kb + 8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) rw[i] = (w_ok && kb + i < a.k) ? w_src[kb + i] : __float2bfloat16_rn(0.0f);
+        }
+    };
+    auto stash = [&](int buf) {
+        if (a.a_op) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ra[i] = dense_a(a, ra[i]);
+        }
+        __nv_bfloat16* as = &As[buf][sr * TC_LD + sk];
+        __nv_bfloat16* ws = &Ws[buf][sr * TC_LD + sk];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+            *reinterpret_cast<__nv_bfloat162*>(as + i) = __floats2bfloat162_rn(ra[i], ra[i + 1]);
+            *reinterpret_cast<__nv_bfloat162*>(ws + i) = __halves2bfloat162(rw[i], rw[i + 1]);
+        }
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[i][j][q] = 0.0f;
+    const uint32_t nk = (a.k + TC_BK - 1) / TC_BK;
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (uint32_t kb = 0; kb < nk; ++kb) {
+        const int cur = kb & 1;
+        if (kb + 1 < nk) fetch((kb + 1) * TC_BK);
+#pragma unroll
+        for (int ks = 0; ks < TC_BK; ks += 16) {
+            uint32_t af[4][4], bf[2][4];
+            // A: matrices (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15) = the MMA's a0..a3
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ldmatrix_x4(af[i], &As[cur][(wm + i * 16 + (lane & 15)) * TC_LD + ks + (lane >> 4) * 8]);
+            // W: two n8 tiles per load: (n 0-7, k 0-7), (n 0-7, k 8-15), (n 8-15, k 0-7), (n 8-15, k 8-15) = b0, b1 of tile 0, b0, b1 of tile 1
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                ldmatrix_x4(bf[j], &Ws[cur][(wn + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * TC_LD + ks + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t b2[2] = {bf[j >> 1][(j & 1) * 2], bf[j >> 1][(j & 1) * 2 + 1]};
+                    mma_bf16_16816(acc[i][j], af[i], b2);
+                }
+        }
+        if (kb + 1 < nk) stash(cur ^ 1);
+        __syncthreads();
+    }
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t p = m0 + wm + i * 16 + g + (q >> 1) * 8;
+                const uint32_t col = n0 + wn + j * 8 + t4 * 2 + (q & 1);
+                if (p < R.count && col < a.n) {
+                    float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + p) * a.ldd + col;
+                    dense_store(a, d, z, R.begin + p, col, acc[i][j][q]);
+                }
+            }
+}
+
 }  // namespace uzu
 
 extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args) {
@@ -451,6 +566,13 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
     }
     if (a.pair_rows) {
         cmd->record_error(UZU_ERROR_UNSUPPORTED, "dense_linear: the paired gated-unit epilogue covers passes of at most 8 rows");
+        return;
+    }
+    static const bool no_tensor128 = getenv("UZU_DENSE_NO_TENSOR128") != nullptr;     // A/B runs
+    if (bf16 && a.m >= 96 && !no_tensor && !no_tensor128) {
+        dim3 grid((a.n + T8_BN - 1) / T8_BN, (a.m + T8_BM - 1) / T8_BM, a.batch);
+        dense_tensor128_kernel<<<grid, 256, 0, cmd->ctx->stream>>>(a);
+        after_launch(cmd, "dense_tensor128_kernel");
         return;
     }
     if (bf16 && a.m >= 32 && !no_tensor) {

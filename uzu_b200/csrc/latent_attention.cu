@@ -142,18 +142,31 @@ __global__ void __launch_bounds__(LA_HEADS * 32) latent_attention_kernel(const u
             // warp adds the 32 partial sums, lane k keeps the score of key k
             const float4* q4 = reinterpret_cast<const float4*>(myq);
             const uint32_t w4 = width / 4;
-            for (uint32_t k = 0; k < n; ++k) {
-                const float4* k4 = reinterpret_cast<const float4*>(tile + (size_t)k * width);
-                float d = 0.0f;
+            // four keys per pass: a query piece is read once for the four rows and the four warp sums overlap
+            for (uint32_t k = 0; k < n; k += 4) {
+                const float4* r0 = reinterpret_cast<const float4*>(tile + (size_t)k * width);
+                const float4* r1 = reinterpret_cast<const float4*>(tile + (size_t)min(k + 1, n - 1) * width);
+                const float4* r2 = reinterpret_cast<const float4*>(tile + (size_t)min(k + 2, n - 1) * width);
+                const float4* r3 = reinterpret_cast<const float4*>(tile + (size_t)min(k + 3, n - 1) * width);
+                float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
                 for (uint32_t c = lane; c < w4; c += 32) {
-                    const float4 x = q4[c], y = k4[c];
-                    d = fmaf(x.x, y.x, d);
-                    d = fmaf(x.y, y.y, d);
-                    d = fmaf(x.z, y.z, d);
-                    d = fmaf(x.w, y.w, d);
+                    const float4 x = q4[c], y0 = r0[c], y1 = r1[c], y2 = r2[c], y3 = r3[c];
+                    d0 = fmaf(x.x, y0.x, d0); d0 = fmaf(x.y, y0.y, d0); d0 = fmaf(x.z, y0.z, d0); d0 = fmaf(x.w, y0.w, d0);
+                    d1 = fmaf(x.x, y1.x, d1); d1 = fmaf(x.y, y1.y, d1); d1 = fmaf(x.z, y1.z, d1); d1 = fmaf(x.w, y1.w, d1);
+                    d2 = fmaf(x.x, y2.x, d2); d2 = fmaf(x.y, y2.y, d2); d2 = fmaf(x.z, y2.z, d2); d2 = fmaf(x.w, y2.w, d2);
+                    d3 = fmaf(x.x, y3.x, d3); d3 = fmaf(x.y, y3.y, d3); d3 = fmaf(x.z, y3.z, d3); d3 = fmaf(x.w, y3.w, d3);
                 }
-                d = warp_sum(d);
-                if (lane == k) s = d * a.scale;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    d0 += __shfl_xor_sync(0xffffffffu, d0, o);
+                    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+                    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+                    d3 += __shfl_xor_sync(0xffffffffu, d3, o);
+                }
+                if (lane == k) s = d0 * a.scale;
+                if (lane == k + 1 && k + 1 < n) s = d1 * a.scale;
+                if (lane == k + 2 && k + 2 < n) s = d2 * a.scale;
+                if (lane == k + 3 && k + 3 < n) s = d3 * a.scale;
             }
         } else if (lane < n) {
             // lane = key. Rows are `width` apart, so the lanes start `lane` channels into the dot product and wrap around: in every step
@@ -233,13 +246,12 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const float* partia
     if (c >= rank) return;
     float v = 0.0f;
     uint32_t s = 0;
-    for (; s + 4 <= splits; s += 4) {
-        const float x0 = part[(size_t)s * (rank + 2) + 2 + c], x1 = part[(size_t)(s + 1) * (rank + 2) + 2 + c];
-        const float x2 = part[(size_t)(s + 2) * (rank + 2) + 2 + c], x3 = part[(size_t)(s + 3) * (rank + 2) + 2 + c];
-        v = fmaf(weight[s], x0, v);
-        v = fmaf(weight[s + 1], x1, v);
-        v = fmaf(weight[s + 2], x2, v);
-        v = fmaf(weight[s + 3], x3, v);
+    for (; s + 8 <= splits; s += 8) {          // eight splits' loads in flight, added in split order
+        float x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) x[u] = part[(size_t)(s + u) * (rank + 2) + 2 + c];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v = fmaf(weight[s + u], x[u], v);
     }
     for (; s < splits; ++s) v = fmaf(weight[s], part[(size_t)s * (rank + 2) + 2 + c], v);
     out[(size_t)blockIdx.x * rank + c] = v * inv_total;
