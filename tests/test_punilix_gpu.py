@@ -370,6 +370,17 @@ def config_b():
     ], norm_groups=1, eps=1e-6, logit_softcap=None)
 
 
+def config_c():
+    """Sizes that fit no vector width: width 90, an odd latent row (21 + 6), head sizes 18 (not a multiple of 4) and 20, odd feed-forwards."""
+    S = synth
+    return S.punilix_config(90, 77, [
+        S.punilix_delta_layer(3, 18, S.punilix_moe_mlp(10, 3, 2, limit=1.5)),
+        S.punilix_latent_layer(3, 7, 6, 9, 21, 11, S.punilix_dense_mlp(50, limit=3.0), scale=0.33, base=50.0,
+                               scaling={"factor": 3.0, "original": 16, "fast": 2.0, "slow": 0.5}),
+        S.punilix_delta_layer(2, 20, None),
+    ], norm_groups=5, eps=1e-5, logit_softcap=4.0)
+
+
 class Pair:
     """A checkpoint on disk, the engine on it and the oracle on the same (bf16-exact) tensors."""
 
@@ -401,7 +412,7 @@ def tokens_for(config, n, seed=0):
     return np.random.default_rng(seed).integers(0, config["vocab"], n).tolist()
 
 
-@pytest.mark.parametrize("make", [config_a, config_b])
+@pytest.mark.parametrize("make", [config_a, config_b, config_c])
 @pytest.mark.parametrize("f32", [True, False])
 def test_prompt_logits_and_layers(ctx, tmp_path, make, f32):
     pr = Pair(ctx, tmp_path, make(), seed=1, f32=f32)
@@ -419,7 +430,7 @@ def test_prompt_logits_and_layers(ctx, tmp_path, make, f32):
     pr.close()
 
 
-@pytest.mark.parametrize("make", [config_a, config_b])
+@pytest.mark.parametrize("make", [config_a, config_b, config_c])
 @pytest.mark.parametrize("f32", [True, False])
 def test_decode_and_portions_match_the_whole_prompt(ctx, tmp_path, make, f32):
     """Prefill + token-by-token decoding, and portions of 2, 3, 1, 33, 2, ... tokens, give the logits of the whole prompt."""
