@@ -9,6 +9,8 @@
 // (per-expert weights: compact rows [off[z], off[z+1]) use weight z, an optional map names the activation row a compact row reads).
 #include <mma.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace uzu {
@@ -72,9 +74,10 @@ __device__ __forceinline__ float clamped_glu_value(float g, float u, float limit
 
 constexpr uint32_t DL_STAGE_FLOATS = 8192;   // activation rows of a group are staged in shared memory when they fit (32 KB)
 
-template <typename TW, int KS, bool PAIR>
-__global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_args a) {
-    __shared__ float part[PAIR ? 2 : 1][8][DL_MAX_ROWS];
+// RMAX = most activation rows of a group (1 for a plain decode step: one accumulator, no row pointers -> more CTAs per SM).
+template <typename TW, int KS, bool PAIR, int RMAX>
+__global__ void __launch_bounds__(256, RMAX == 1 ? 4 : 2) dense_rows_kernel(const uzu_dense_linear_args a) {
+    __shared__ float part[PAIR ? 2 : 1][8][RMAX];
     __shared__ __align__(16) float a_s[DL_STAGE_FLOATS];
     const uint32_t z = blockIdx.y;
     const int lane = threadIdx.x & 31;
@@ -113,9 +116,9 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
     const uint32_t* map = reinterpret_cast<const uint32_t*>(a.rows_map);
     // the group's activation rows, with the A operation applied, go to shared memory once per CTA when they fit
     const bool staged = vec_ok && (size_t)R.count * a.k <= DL_STAGE_FLOATS;
-    const float* arow[DL_MAX_ROWS];
+    const float* arow[RMAX];
 #pragma unroll
-    for (int r = 0; r < DL_MAX_ROWS; ++r) {
+    for (int r = 0; r < RMAX; ++r) {
         const uint32_t p = R.begin + ((uint32_t)r < R.count ? r : 0);
         arow[r] = reinterpret_cast<const float*>(a.a) + (size_t)z * a.a_z_stride + (size_t)(map ? map[p] : p) * a.lda;
     }
@@ -131,11 +134,11 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
         }
         __syncthreads();
     }
-    float acc[DL_MAX_ROWS], acc2[PAIR ? DL_MAX_ROWS : 1];
+    float acc[RMAX], acc2[PAIR ? RMAX : 1];
 #pragma unroll
-    for (int r = 0; r < DL_MAX_ROWS; ++r) acc[r] = 0.0f;
+    for (int r = 0; r < RMAX; ++r) acc[r] = 0.0f;
 #pragma unroll
-    for (int r = 0; r < (PAIR ? DL_MAX_ROWS : 1); ++r) acc2[r] = 0.0f;
+    for (int r = 0; r < (PAIR ? RMAX : 1); ++r) acc2[r] = 0.0f;
     if (!col_ok) {
         // nothing to sum; the warp still meets the others at the barrier below
     } else if (vec_ok) {
@@ -150,7 +153,7 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
                 unpack_weights<VEC, TW>(cur[u], wf);
                 if constexpr (PAIR) unpack_weights<VEC, TW>(cur2[u], wf2);
 #pragma unroll
-                for (int r = 0; r < DL_MAX_ROWS; ++r) {
+                for (int r = 0; r < RMAX; ++r) {
                     if ((uint32_t)r < R.count) {
 #pragma unroll
                         for (int i = 0; i < VEC; i += 4) {
@@ -186,7 +189,7 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
             const float wv = w_to_f32<TW>(w[k0]);
             const float wv2 = PAIR ? w_to_f32<TW>(w2[k0]) : 0.0f;
 #pragma unroll
-            for (int r = 0; r < DL_MAX_ROWS; ++r)
+            for (int r = 0; r < RMAX; ++r)
                 if ((uint32_t)r < R.count) {
                     const float x = dense_a(a, arow[r][k0]);
                     acc[r] = fmaf(x, wv, acc[r]);
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(256) dense_rows_kernel(const uzu_dense_linear_
         else dense_store(a, d, z, R.begin + r, col, s);
     };
 #pragma unroll
-    for (int r = 0; r < DL_MAX_ROWS; ++r) {
+    for (int r = 0; r < RMAX; ++r) {
         if ((uint32_t)r < R.count) {          // uniform over the warp
             const float s = warp_sum(acc[r]);
             float s2 = 0.0f;
@@ -322,7 +325,7 @@ __global__ void __launch_bounds__(128) dense_tensor_kernel(const uzu_dense_linea
     const bool a_vec = (a.lda % 4 == 0) && ((a.a & 15) == 0) && (a.a_z_stride % 4 == 0) && (a.k % 4 == 0);
     const bool w_vec = (a.k % 8 == 0) && ((a.w & 15) == 0) && (a.w_z_stride % 8 == 0);
     float ra[16];
-    __nv_bfloat16 rw[16];
+    __align__(16) __nv_bfloat16 rw[16];
     auto fetch = [&](uint32_t k0) {
         const uint32_t kb = k0 + sk;
         if (a_ok && a_vec && kb + 16 <= a.k) {
@@ -441,7 +444,7 @@ __global__ void __launch_bounds__(256) dense_tensor128_kernel(const uzu_dense_li
     const bool a_vec = (a.lda % 4 == 0) && ((a.a & 15) == 0) && (a.a_z_stride % 4 == 0) && (a.k % 4 == 0);
     const bool w_vec = (a.k % 8 == 0) && ((a.w & 15) == 0) && (a.w_z_stride % 8 == 0);
     float ra[16];
-    __nv_bfloat16 rw[16];
+    __align__(16) __nv_bfloat16 rw[16];
     auto fetch = [&](uint32_t k0) {
         const uint32_t kb = k0 + sk;
         if (a_ok && a_vec && kb + 16 <= a.k) {
@@ -467,13 +470,19 @@ __global__ void __launch_bounds__(256) dense_tensor128_kernel(const uzu_dense_li
 #pragma unroll
             for (int i = 0; i < 16; ++i) ra[i] = dense_a(a, ra[i]);
         }
-        __nv_bfloat16* as = &As[buf][sr * TC_LD + sk];
-        __nv_bfloat16* ws = &Ws[buf][sr * TC_LD + sk];
+        // rows are 80 bytes apart and a thread's half row starts at byte 0 or 32: 16-byte stores
+        uint32_t pa2[8];
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-            *reinterpret_cast<__nv_bfloat162*>(as + i) = __floats2bfloat162_rn(ra[i], ra[i + 1]);
-            *reinterpret_cast<__nv_bfloat162*>(ws + i) = __halves2bfloat162(rw[i], rw[i + 1]);
+        for (int i = 0; i < 8; ++i) {
+            const __nv_bfloat162 v = __floats2bfloat162_rn(ra[2 * i], ra[2 * i + 1]);
+            pa2[i] = *reinterpret_cast<const uint32_t*>(&v);
         }
+        uint4* as = reinterpret_cast<uint4*>(&As[buf][sr * TC_LD + sk]);
+        uint4* ws = reinterpret_cast<uint4*>(&Ws[buf][sr * TC_LD + sk]);
+        as[0] = make_uint4(pa2[0], pa2[1], pa2[2], pa2[3]);
+        as[1] = make_uint4(pa2[4], pa2[5], pa2[6], pa2[7]);
+        ws[0] = *reinterpret_cast<const uint4*>(&rw[0]);
+        ws[1] = *reinterpret_cast<const uint4*>(&rw[8]);
     };
     float acc[4][4][4];
 #pragma unroll
@@ -552,16 +561,24 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         const int ks = (features >= 4096 || a.k < 2 * sweep) ? 1 : (features >= 2048 || a.k < 4 * sweep) ? 2 : 4;
         dim3 grid((a.n * ks + 7) / 8, a.batch);
         auto go = [&](auto kernel) { launch(cmd, "dense_rows_kernel", kernel, grid, dim3(256), 0, a); };
-        const bool pair = a.pair_rows != 0;
-        if (bf16) {
-            if (ks == 1) pair ? go(dense_rows_kernel<__nv_bfloat16, 1, true>) : go(dense_rows_kernel<__nv_bfloat16, 1, false>);
-            else if (ks == 2) pair ? go(dense_rows_kernel<__nv_bfloat16, 2, true>) : go(dense_rows_kernel<__nv_bfloat16, 2, false>);
-            else pair ? go(dense_rows_kernel<__nv_bfloat16, 4, true>) : go(dense_rows_kernel<__nv_bfloat16, 4, false>);
-        } else {
-            if (ks == 1) pair ? go(dense_rows_kernel<float, 1, true>) : go(dense_rows_kernel<float, 1, false>);
-            else if (ks == 2) pair ? go(dense_rows_kernel<float, 2, true>) : go(dense_rows_kernel<float, 2, false>);
-            else pair ? go(dense_rows_kernel<float, 4, true>) : go(dense_rows_kernel<float, 4, false>);
-        }
+        auto pick = [&](auto tw, auto ks_c, auto pair_c) {
+            using TW = decltype(tw);
+            constexpr int KSv = decltype(ks_c)::value;
+            constexpr bool PAIRv = decltype(pair_c)::value;
+            if (a.m == 1) go(dense_rows_kernel<TW, KSv, PAIRv, 1>);
+            else go(dense_rows_kernel<TW, KSv, PAIRv, DL_MAX_ROWS>);
+        };
+        auto by_pair = [&](auto tw, auto ks_c) {
+            if (a.pair_rows) pick(tw, ks_c, std::true_type{});
+            else pick(tw, ks_c, std::false_type{});
+        };
+        auto by_ks = [&](auto tw) {
+            if (ks == 1) by_pair(tw, std::integral_constant<int, 1>{});
+            else if (ks == 2) by_pair(tw, std::integral_constant<int, 2>{});
+            else by_pair(tw, std::integral_constant<int, 4>{});
+        };
+        if (bf16) by_ks(__nv_bfloat16{});
+        else by_ks(float{});
         return;
     }
     if (a.pair_rows) {
