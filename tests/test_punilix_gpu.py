@@ -116,6 +116,52 @@ def test_dense_linear_heads_and_accumulate(ctx, m):
     close(got, ref, 3e-6, "z-batched dense linear")
 
 
+@pytest.mark.parametrize("m", [1, 4, 8, 40, 130])
+@pytest.mark.parametrize("f32_weights", [True, False])
+def test_dense_linear_operand_and_epilogue_options(ctx, m, f32_weights):
+    """tanh applied to A as it is read; the sigmoid gate on the product; the paired gated-unit form (<= 8 rows) against the two-launch form."""
+    rng = np.random.default_rng(100 + m)
+    n, k = 48, 64
+    a = rng.standard_normal((m, k), dtype=np.float32)
+    w = synth.st_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((2 * n, k), dtype=np.float32) / 4))
+    gate = rng.standard_normal((m, n + 3), dtype=np.float32)
+    wb = ctx.upload(np.ascontiguousarray(w) if f32_weights else synth.f32_to_bf16_bits(w))
+    ab, gb = ctx.upload(a), ctx.upload(gate)
+    dt = B.DT_F32 if f32_weights else B.DT_BF16
+    rounds_a = (not f32_weights) and m >= 32             # the tensor-pipe kernels round the (transformed) activations to bf16
+    bf = lambda x: synth.st_bits_to_f32(synth.f32_to_bf16_bits(np.asarray(x, np.float32)))
+    # tanh on A + sigmoid gate on D
+    db = ctx.upload(np.zeros((m, n), np.float32))
+    args = B.DenseLinearArgs(a=ab.ptr, w=wb.ptr, d=db.ptr, gate=gb.ptr, gate_ld=n + 3, m=m, n=n, k=k, lda=k, ldd=n, batch=1, weights_dt=dt, scale=1.0, a_op=1)
+    run(ctx, "uzu_dense_linear_encode", C.byref(args))
+    ta = torch.tanh(t64(a))
+    if rounds_a:
+        ta = t64(bf(ta.numpy()))
+    ref = (ta @ t64(w[:n]).T) * torch.sigmoid(t64(gate[:, :n]))
+    close(db.numpy(np.float32, (m, n)), ref.numpy(), 3e-3 if rounds_a else 5e-6, "tanh operand + gate epilogue")   # a bf16 rounding of tanh may fall the other way
+    # paired gated unit
+    if m <= 8:
+        db2 = ctx.upload(np.zeros((m, n), np.float32))
+        args = B.DenseLinearArgs(a=ab.ptr, w=wb.ptr, d=db2.ptr, m=m, n=n, k=k, lda=k, ldd=n, batch=1, weights_dt=dt, scale=1.0, pair_rows=n,
+                                 glu_limit=0.7, glu_alpha=1.702)
+        run(ctx, "uzu_dense_linear_encode", C.byref(args))
+        ref = P.clamped_glu(t64(a), t64(w[:n]), t64(w[n:]), torch.eye(n, dtype=F64), 0.7)
+        close(db2.numpy(np.float32, (m, n)), ref.numpy(), 5e-6, "paired gated unit")
+
+
+def test_unary_and_residual_add(ctx):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((7, 20), dtype=np.float32)
+    bx, bo = ctx.upload(x), ctx.upload(np.zeros((7, 9), np.float32))
+    run(ctx, "uzu_unary_f32_encode", bx.ptr + 4 * 3, 20, bo.ptr, 9, 7, 9, 0)          # tanh of columns 3..11
+    close(bo.numpy(np.float32, (7, 9)), np.tanh(x[:, 3:12].astype(np.float64)), 2e-6, "tanh")
+    r, a, b = (rng.standard_normal(150, dtype=np.float32) for _ in range(3))
+    br, ba, bb = ctx.upload(r), ctx.upload(a), ctx.upload(b)
+    run(ctx, "uzu_residual_add_encode", br.ptr, ba.ptr, bb.ptr, 150)
+    run(ctx, "uzu_residual_add_encode", br.ptr, ba.ptr, 0, 150)
+    close(br.numpy(np.float32, (150,)), r.astype(np.float64) + 2 * a.astype(np.float64) + b, 2e-6, "residual add")
+
+
 @pytest.mark.parametrize("rows,top,experts", [(1, 1, 4), (5, 3, 7), (64, 2, 5), (200, 4, 16)])
 def test_table_route_and_expert_products(ctx, rows, top, experts):
     """Router lists + grouped products + combine against a per-token loop; some experts get no token, some many."""
