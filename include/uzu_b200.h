@@ -469,6 +469,8 @@ typedef struct uzu_dense_linear_args {
     uint64_t rows_map;             /* optional u32 [rows] (device) */
     uint64_t a_z_stride, w_z_stride, d_z_stride;
     uint64_t gate;                 /* optional f32 [rows, gate_ld]: the product is multiplied by sigmoid(gate[row, z*d_z_stride + col]) */
+    uint64_t workspace;            /* optional bf16 [m, k] scratch: with it, plain bf16 products of >= 128 rows (k a multiple of 64) run on
+                                      tcgen05 tensor cores with accumulators in tensor memory (A is converted into the scratch first) */
     uint32_t m, n, k, lda, ldd, batch;   /* batch = number of z (>= 1) */
     uint32_t weights_dt, accumulate;
     float scale;                   /* applied to the product before gate / bias / accumulation */
@@ -480,6 +482,8 @@ typedef struct uzu_dense_linear_args {
     float glu_limit, glu_alpha;
 } uzu_dense_linear_args;
 UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
+/* 0, or the code of the first bounded barrier wait that ran out inside a tensor-memory dense product (the kernel gives up and returns) */
+UZU_API unsigned int uzu_debug_dense_umma_error(void);
 
 /* RMS norm in `groups` equal consecutive parts of a row: part / sqrt(mean(part^2) + epsilon), whole row times scales.
  * input f32 [rows, in_stride] (first n columns), optional row gather, output f32 [rows, out_stride]. groups = 1 is the plain RMS norm. */

@@ -116,6 +116,30 @@ def test_dense_linear_heads_and_accumulate(ctx, m):
     close(got, ref, 3e-6, "z-batched dense linear")
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (130, 200, 128), (257, 75, 192), (1024, 384, 1024), (300, 64, 2048)])
+def test_dense_linear_tensor_memory_form(ctx, lib, m, n, k):
+    """With a bf16 workspace, plain products of >= 128 rows run on tcgen05 (tile edges in m and n, 1 .. 32 K blocks, accumulate, gate, tanh)."""
+    rng = np.random.default_rng(m + n + k)
+    a = rng.standard_normal((m, k + 4), dtype=np.float32)              # rows wider than k
+    w = synth.st_bits_to_f32(synth.f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32)))
+    d0 = rng.standard_normal((m, n + 5), dtype=np.float32)
+    gate = rng.standard_normal((m, n), dtype=np.float32)
+    ab, wb, db, gb = ctx.upload(a), ctx.upload(synth.f32_to_bf16_bits(w)), ctx.upload(d0), ctx.upload(gate)
+    ws = ctx.buffer(m * k * 2, B.BUFFER_DEVICE)
+    args = B.DenseLinearArgs(a=ab.ptr, w=wb.ptr, d=db.ptr, gate=gb.ptr, gate_ld=n, workspace=ws.ptr, m=m, n=n, k=k, lda=k + 4, ldd=n + 5, batch=1,
+                             weights_dt=B.DT_BF16, accumulate=1, scale=0.5, a_op=1)
+    with ctx.command_buffer("umma") as cmd:
+        cmd.encode("uzu_dense_linear_encode", C.byref(args))
+    assert cmd.launches == 2                                           # the conversion and the tensor-memory kernel, not the mma.sync form
+    assert lib.uzu_debug_dense_umma_error() == 0
+    ta = t64(synth.st_bits_to_f32(synth.f32_to_bf16_bits(np.tanh(a[:, :k].astype(np.float64)).astype(np.float32))))
+    ref = d0.astype(np.float64)
+    ref[:, :n] += (0.5 * (ta @ t64(w).T) * torch.sigmoid(t64(gate))).numpy()
+    got = db.numpy(np.float32, d0.shape)
+    assert np.array_equal(got[:, n:], d0[:, n:])                       # columns past n are untouched
+    close(got[:, :n], ref[:, :n], 3e-3, "tensor-memory dense product")
+
+
 @pytest.mark.parametrize("m", [1, 4, 8, 40, 130])
 @pytest.mark.parametrize("f32_weights", [True, False])
 def test_dense_linear_operand_and_epilogue_options(ctx, m, f32_weights):

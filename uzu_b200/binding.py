@@ -133,7 +133,7 @@ FusedLinearArgs = _struct("uzu_fused_linear_args", [
 # kernels of the parallel-block family (f32 activations, dense bf16 / f32 weights)
 DenseLinearArgs = _struct("uzu_dense_linear_args", [
     ("a", u64), ("w", u64), ("d", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64),
-    ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64), ("gate", u64),
+    ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64), ("gate", u64), ("workspace", u64),
     ("m", u32), ("n", u32), ("k", u32), ("lda", u32), ("ldd", u32), ("batch", u32),
     ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("a_op", u32), ("gate_ld", u32), ("pair_rows", u32),
     ("glu_limit", f32), ("glu_alpha", f32)])
@@ -200,7 +200,7 @@ uzu_engine_speculation_supported uzu_engine_trie_pass uzu_engine_trie_accept uzu
 uzu_activation_transform_validate uzu_dense_linear_encode uzu_group_rms_norm_encode uzu_embedding_f32_encode uzu_clamped_glu_encode
 uzu_unary_f32_encode uzu_residual_add_encode uzu_logit_cap_f32_encode uzu_table_route_encode uzu_routed_combine_encode
 uzu_general_delta_encode uzu_head_norm_gate_encode uzu_latent_prepare_encode uzu_latent_attention_encode
-uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs""".split()
+uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs uzu_debug_dense_umma_error""".split()
 
 _lib = None
 
@@ -333,6 +333,7 @@ def load() -> C.CDLL:
         "uzu_fused_linear_supported": (C.c_int, [vp, C.POINTER(FusedLinearArgs)]),
         "uzu_fused_linear_encode": (None, [vp, C.POINTER(FusedLinearArgs)]),
         "uzu_dense_linear_encode": (None, [vp, C.POINTER(DenseLinearArgs)]),
+        "uzu_debug_dense_umma_error": (C.c_uint, []),
         "uzu_group_rms_norm_encode": (None, [vp, C.POINTER(GroupRmsNormArgs)]),
         "uzu_embedding_f32_encode": (None, [vp, u64, u64, u32, u64, u32, u32, u32]),
         "uzu_clamped_glu_encode": (None, [vp, u64, u64, u32, u32, f32, f32]),

@@ -38,6 +38,7 @@ SOURCES = {
     "deltanet_prefill.cu": ["-fmad=false"],
     "decode_mega.cu": [],
     "dense_linear.cu": [],
+    "dense_umma.cu": [],
     "residual_f32.cu": [],
     "general_delta.cu": [],
     "latent_attention.cu": [],

@@ -15,6 +15,10 @@
 
 namespace uzu {
 
+// tcgen05 form of the plain bf16 product (dense_umma.cu)
+bool dense_umma_applicable(const uzu_dense_linear_args& a);
+void encode_dense_umma(uzu_command_buffer* cmd, const uzu_dense_linear_args& a);
+
 struct DenseRows {
     uint32_t begin, count;
 };
@@ -583,6 +587,10 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
     }
     if (a.pair_rows) {
         cmd->record_error(UZU_ERROR_UNSUPPORTED, "dense_linear: the paired gated-unit epilogue covers passes of at most 8 rows");
+        return;
+    }
+    if (dense_umma_applicable(a)) {
+        encode_dense_umma(cmd, a);
         return;
     }
     static const bool no_tensor128 = getenv("UZU_DENSE_NO_TENSOR128") != nullptr;     // A/B runs

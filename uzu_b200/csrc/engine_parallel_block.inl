@@ -259,7 +259,7 @@ constexpr uint32_t kSplitRows = 256;   // query rows x key splits of one latent-
 static void create_parallel_block_scratch(uzu_engine* e) {
     if (!e->parallel_block) return;
     const uint32_t W = e->model_dim;
-    uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1;
+    uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1, kmax = e->model_dim;
     for (const Layer& L : e->layers) {
         if (L.kind == MixGeneralDelta) {
             const uint32_t HD = L.gd.heads * L.gd.dim;
@@ -268,6 +268,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             wide = std::max(wide, HD);
             mixed = std::max(mixed, HD);
             gated = std::max(gated, HD);
+            kmax = std::max({kmax, HD, L.gd.decay_rank});
         } else {
             const LatentAttentionLayer& A = L.la;
             proj = std::max(proj, A.in.rows);
@@ -277,10 +278,12 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             mixed = std::max(mixed, A.heads * A.rank);
             gated = std::max(gated, A.heads * A.vdim);
             partial = std::max(partial, A.heads * (A.rank + 2));
+            kmax = std::max({kmax, A.q_rank, A.heads * A.vdim});
         }
         if (L.gmlp.kind != GatedMlp::None) {
             gu = std::max(gu, 2 * L.gmlp.f);
             act = std::max(act, L.gmlp.f);
+            kmax = std::max(kmax, L.gmlp.f);
             top = std::max(top, L.gmlp.top);
             experts = std::max(experts, L.gmlp.experts);
         }
@@ -290,6 +293,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     auto& P = e->pb;
     P.resid = dev(R * W * 4);
     P.normed = dev(R * W * 4);
+    P.operand_bf16 = dev(R * kmax * 2);     // bf16 copy of a prompt pass's activation rows for the tensor-memory products
     P.proj = dev(R * proj * 4);
     P.lat = dev(R * lat * 4);
     P.wide = dev(R * wide * 4);
@@ -312,6 +316,7 @@ static uzu_dense_linear_args dense_args(const uzu_engine* e, const DenseMatrix& 
     x.a = a; x.w = m.w.ptr(); x.d = d;
     x.m = rows; x.n = m.rows; x.k = m.cols; x.lda = m.cols; x.ldd = m.rows; x.batch = 1;
     x.weights_dt = e->store_dt; x.scale = 1.0f;
+    x.workspace = e->pb.operand_bf16.ptr();
     return x;
 }
 
