@@ -527,6 +527,8 @@ UZU_API void uzu_routed_combine_encode(uzu_command_buffer* cmd, uint64_t pairs, 
 typedef struct uzu_general_delta_args {
     uint64_t r, k, v, rate_logit, decay_logit;
     uint64_t rate_bias, decay_bias;          /* f32 [heads*dim] */
+    uint64_t unit;                           /* optional f32 [rows, heads*dim] scratch: passes of >= 4 rows then form decay, rate * unit key and unit
+                                                key for all rows in one parallel launch first, IN PLACE over decay_logit / rate_logit */
     uint64_t state, out;                     /* out f32 [rows, heads*dim] */
     uint32_t r_stride, k_stride, v_stride, rate_stride, decay_stride;
     uint32_t rows, heads, dim;

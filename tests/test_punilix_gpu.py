@@ -223,13 +223,15 @@ def test_table_route_and_expert_products(ctx, rows, top, experts):
     close(bo.numpy(np.float32, (rows, W)), ref.numpy(), 5e-6, "table-routed experts")
 
 
-def general_delta_gpu(ctx, r, k, v, rate, decay, rate_b, decay_b, state, heads, dim):
+def general_delta_gpu(ctx, r, k, v, rate, decay, rate_b, decay_b, state, heads, dim, prepared=False):
     rows = r.shape[0]
     bufs = [ctx.upload(np.ascontiguousarray(x, np.float32)) for x in (r, k, v, rate, decay, rate_b, decay_b, state)]
     out = ctx.upload(np.zeros((rows, heads * dim), np.float32))
     hd = heads * dim
+    hd = heads * dim
+    unit = ctx.upload(np.zeros((rows, hd), np.float32)) if prepared else None      # with it, passes of >= 4 rows form their vectors up front
     a = B.GeneralDeltaArgs(r=bufs[0].ptr, k=bufs[1].ptr, v=bufs[2].ptr, rate_logit=bufs[3].ptr, decay_logit=bufs[4].ptr, rate_bias=bufs[5].ptr,
-                           decay_bias=bufs[6].ptr, state=bufs[7].ptr, out=out.ptr, r_stride=hd, k_stride=hd, v_stride=hd, rate_stride=hd,
+                           decay_bias=bufs[6].ptr, unit=unit.ptr if unit else 0, state=bufs[7].ptr, out=out.ptr, r_stride=hd, k_stride=hd, v_stride=hd, rate_stride=hd,
                            decay_stride=hd, rows=rows, heads=heads, dim=dim)
     run(ctx, "uzu_general_delta_encode", C.byref(a))
     return out.numpy(np.float32, (rows, hd)), bufs[7].numpy(np.float32, state.shape)
@@ -260,10 +262,11 @@ def test_general_delta_kernel(ctx, rows, heads, dim):
     r, k, v, rate, decay = (rng.standard_normal((rows, hd), dtype=np.float32) for _ in range(5))
     rate_b, decay_b = rng.standard_normal(hd, dtype=np.float32), rng.standard_normal(hd, dtype=np.float32)
     state = rng.standard_normal((heads, dim, dim), dtype=np.float32)
-    got, got_state = general_delta_gpu(ctx, r, k, v, rate, decay, rate_b, decay_b, state, heads, dim)
     ref, ref_state = general_delta_plain(r, k, v, rate, decay, rate_b, decay_b, state, heads, dim)
-    close(got, ref, 1e-5, "generalized delta output")
-    close(got_state, ref_state, 1e-5, "generalized delta state")
+    for prepared in (False, True):
+        got, got_state = general_delta_gpu(ctx, r, k, v, rate, decay, rate_b, decay_b, state, heads, dim, prepared)
+        close(got, ref, 1e-5, "generalized delta output")
+        close(got_state, ref_state, 1e-5, "generalized delta state")
 
 
 def test_general_delta_one_launch_equals_token_by_token(ctx):

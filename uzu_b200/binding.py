@@ -147,7 +147,7 @@ TableRouteArgs = _struct("uzu_table_route_args", [
     ("rows", u32), ("top", u32), ("experts", u32), ("vocab", u32)])
 
 GeneralDeltaArgs = _struct("uzu_general_delta_args", [
-    ("r", u64), ("k", u64), ("v", u64), ("rate_logit", u64), ("decay_logit", u64), ("rate_bias", u64), ("decay_bias", u64),
+    ("r", u64), ("k", u64), ("v", u64), ("rate_logit", u64), ("decay_logit", u64), ("rate_bias", u64), ("decay_bias", u64), ("unit", u64),
     ("state", u64), ("out", u64),
     ("r_stride", u32), ("k_stride", u32), ("v_stride", u32), ("rate_stride", u32), ("decay_stride", u32),
     ("rows", u32), ("heads", u32), ("dim", u32)])

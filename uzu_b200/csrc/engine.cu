@@ -448,7 +448,7 @@ struct uzu_engine {
     DenseMatrix pb_embed, pb_head;
     Buf pb_final_norm;
     struct PbScratch {
-        Buf resid, normed, operand_bf16, proj, lat, wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
+        Buf resid, normed, operand_bf16, proj, lat, wide, lat_wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;
         bool dump = false;

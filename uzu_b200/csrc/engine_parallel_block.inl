@@ -297,6 +297,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     P.proj = dev(R * proj * 4);
     P.lat = dev(R * lat * 4);
     P.wide = dev(R * wide * 4);
+    P.lat_wide = dev(R * wide * 4);     // unit keys of a prompt pass (generalized delta rule)
     P.query = dev(R * query * 4);
     P.attn_partial = dev((size_t)kSplitRows * partial * 4);
     P.mixed = dev(R * mixed * 4);
@@ -348,7 +349,7 @@ static void encode_general_delta(uzu_engine* e, uzu_command_buffer* cmd, const L
     ga.r = P.proj.ptr(); ga.k = P.proj.ptr() + (uint64_t)HD * 4; ga.v = P.proj.ptr() + (uint64_t)2 * HD * 4;
     ga.rate_logit = P.proj.ptr() + (uint64_t)3 * HD * 4; ga.decay_logit = P.wide.ptr();
     ga.rate_bias = G.rate_bias.ptr(); ga.decay_bias = G.decay_bias.ptr();
-    ga.state = S.ssm_state.ptr(); ga.out = P.mixed.ptr();
+    ga.state = S.ssm_state.ptr(); ga.out = P.mixed.ptr(); ga.unit = P.lat_wide.ptr();
     ga.r_stride = ga.k_stride = ga.v_stride = ga.rate_stride = ld; ga.decay_stride = HD;
     ga.rows = m; ga.heads = G.heads; ga.dim = G.dim;
     uzu_general_delta_encode(cmd, &ga);
