@@ -450,7 +450,7 @@ UZU_API void uzu_delta_net_fused_update_encode(uzu_command_buffer* cmd, const uz
  * instead of one decode-kernel launch per token. NOT yet run on hardware (round 1). */
 UZU_API void uzu_debug_set_delta_prefill(int mode);
 
-/* ---- Kernels of the parallel-block family (Punilix): 32-bit residual stream, dense (unquantised) weights ------------------- *
+/* ---- Kernels of the parallel-block families (Punilix, Gamanex): 32-bit residual stream, dense (unquantised) weights ------------------- *
  * Extensions (the reference has no such model). Activations between kernels are f32; weights and the latent KV cache carry the
  * engine's storage type (`UZU_DT_BF16` or `UZU_DT_F32`); sums, norms, scores, decays and recurrent state are f32 always. */
 
@@ -474,23 +474,30 @@ typedef struct uzu_dense_linear_args {
     uint32_t m, n, k, lda, ldd, batch;   /* batch = number of z (>= 1) */
     uint32_t weights_dt, accumulate;
     float scale;                   /* applied to the product before gate / bias / accumulation */
-    uint32_t a_op;                 /* applied to every A element as it is read: 0 none, 1 tanh */
+    uint32_t a_op;                 /* applied to every A element as it is read: 0 none, 1 tanh, 2 max(x, 0)^2 */
     uint32_t gate_ld;
     uint32_t pair_rows;            /* m <= 8 only. Non-zero: W has a second block of rows `pair_rows` below the first; feature col forms
                                       g = A.W[col], u = A.W[col + pair_rows] and stores the clamped gated unit
                                       min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1) */
     float glu_limit, glu_alpha;
+    uint32_t glu_kind;             /* paired epilogue: 0 the clamped unit above, 1 g * sigmoid(g) * u */
+    uint32_t reserved0;
+    uint64_t gate_bias;            /* optional f32 [n] (with gate): sigmoid(gate[row, col] + gate_bias[col]) */
+    uint64_t col_scale;            /* optional f32 [n]: the product is multiplied by col_scale[col] (a per-channel layer scale) */
 } uzu_dense_linear_args;
 UZU_API void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense_linear_args* args);
 /* 0, or the code of the first bounded barrier wait that ran out inside a tensor-memory dense product (the kernel gives up and returns) */
 UZU_API unsigned int uzu_debug_dense_umma_error(void);
 
 /* RMS norm in `groups` equal consecutive parts of a row: part / sqrt(mean(part^2) + epsilon), whole row times scales.
- * input f32 [rows, in_stride] (first n columns), optional row gather, output f32 [rows, out_stride]. groups = 1 is the plain RMS norm. */
+ * input f32 [rows, in_stride] (first n columns), optional row gather, output f32 [rows, out_stride]. groups = 1 is the plain RMS norm.
+ * With output2 the same normalised row is stored a second time, times scales2 (two sublayers that norm the same input with their own
+ * weights share the sum of squares). */
 typedef struct uzu_group_rms_norm_args {
     uint64_t input, scales /* f32 [n], 0 = none */, output, row_indices /* optional u32 [rows] */;
     uint32_t rows, n, groups, in_stride, out_stride;
     float epsilon;
+    uint64_t scales2, output2;     /* optional second scaled copy, f32 [rows, out_stride] */
 } uzu_group_rms_norm_args;
 UZU_API void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_rms_norm_args* args);
 
@@ -504,6 +511,8 @@ UZU_API void uzu_group_rms_norm_encode(uzu_command_buffer* cmd, const uzu_group_
 UZU_API void uzu_embedding_f32_encode(uzu_command_buffer* cmd, uint64_t token_ids, uint64_t table, uint32_t weights_dt, uint64_t output,
                                       uint32_t rows, uint32_t vocab, uint32_t n);
 UZU_API void uzu_clamped_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f, float limit, float alpha);
+/*   silu_glu:        out = g * sigmoid(g) * u, same operand layout as clamped_glu */
+UZU_API void uzu_silu_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f);
 UZU_API void uzu_unary_f32_encode(uzu_command_buffer* cmd, uint64_t input, uint32_t in_stride, uint64_t output, uint32_t out_stride,
                                   uint32_t rows, uint32_t n, uint32_t op);
 UZU_API void uzu_residual_add_encode(uzu_command_buffer* cmd, uint64_t x, uint64_t a, uint64_t b, uint32_t length);
@@ -519,6 +528,54 @@ typedef struct uzu_table_route_args {
 UZU_API void uzu_table_route_encode(uzu_command_buffer* cmd, const uzu_table_route_args* args);
 UZU_API void uzu_routed_combine_encode(uzu_command_buffer* cmd, uint64_t pairs, uint64_t pair_pos, uint64_t output, uint32_t rows, uint32_t top,
                                        uint32_t n, float weight, uint32_t accumulate);
+
+/* Learned router: per row the `top` largest of logits[r, 0:experts] + bias (the lower index wins a tie), weights = softmax over the
+ * chosen logits only (f32). Builds the same expert-sorted pair lists as table_route, plus pair_weight f32 [rows*top] indexed like
+ * pair_pos (row * top + slot, slot 0 = the largest logit). */
+typedef struct uzu_topk_route_args {
+    uint64_t logits /* f32 [rows, logits_stride] */, bias /* optional f32 [experts] */, group_offsets, rows_map, pair_pos, pair_weight;
+    uint32_t rows, top, experts, logits_stride;
+} uzu_topk_route_args;
+UZU_API void uzu_topk_route_encode(uzu_command_buffer* cmd, const uzu_topk_route_args* args);
+
+/* out[r, c] (+)= weight * col_scale[c] * sigmoid(gate[r, c] + gate_bias[c]) * sum_slot pair_weight[r*top + slot] * pairs[pair_pos[r*top + slot], c];
+ * pair_weight, gate (+ gate_bias) and col_scale are optional. */
+typedef struct uzu_routed_combine_args {
+    uint64_t pairs, pair_pos, pair_weight, gate, gate_bias, col_scale, output;
+    uint32_t rows, top, n, gate_ld, accumulate;
+    float weight;
+} uzu_routed_combine_args;
+UZU_API void uzu_routed_combine_gated_encode(uzu_command_buffer* cmd, const uzu_routed_combine_args* args);
+
+/* Sigmoid attention (no softmax, no rotation), cache side and query side of one pass. Per token row t at position p = prefix + t (prefix
+ * read from dynamic_position when non-zero):
+ *   query[t, :] = rms(q[t, 0:q_n]) * q_scales * (1 + temp_coef * ln(floor((p + 1) / temp_every) + 1))     (f32 [rows, q_n]; temp_every = 0: no factor)
+ *   keys[p, :]  = rms(k[t, 0:k_n]) * k_scales,  values[p, :] = v[t, 0:v_n]                                  (cache_dt; k = 0: the layer reads another layer's cache)
+ * Both norms run over the whole projection (all heads at once). */
+typedef struct uzu_sigmoid_attention_prepare_args {
+    uint64_t q, k, v, q_scales, k_scales, query, keys, values, dynamic_position;
+    uint32_t rows, q_n, k_n, v_n, q_stride, k_stride, v_stride, prefix, cache_dt, temp_every;
+    float epsilon, temp_coef;
+} uzu_sigmoid_attention_prepare_args;
+UZU_API void uzu_sigmoid_attention_prepare_encode(uzu_command_buffer* cmd, const uzu_sigmoid_attention_prepare_args* args);
+
+/* Causal sigmoid attention of `rows` queries (positions prefix + t) over cached keys [positions, kv_heads*dim] / values [positions,
+ * kv_heads*vdim]; query head h reads key / value head h / (heads / kv_heads):
+ *   s(t, h, j) = scale * query[t, h, :] . keys[j, g, :] - dist_r1[h] * ln(1 + dist_r2[h] * (p - j)) + head_bias[h],   j <= p
+ *   out[t, h, :] = sum_j sigmoid(s) * values[j, g, :]        (f32 [rows, heads*vdim]; weights are not normalised over j)
+ * Scores, weights and sums are f32. bf16 caches with rows >= 16 and dim, vdim multiples of 16 up to 128 run on the tensor pipe: query
+ * and weight each as a sum of two bf16 numbers (hi + lo), so their rounding stays below 2^-16. */
+typedef struct uzu_sigmoid_attention_args {
+    uint64_t query, keys, values, out, dynamic_position;
+    uint64_t dist_r1, dist_r2, head_bias;   /* optional f32 [heads] */
+    uint64_t partials;             /* scratch f32 [rows, heads, splits, vdim] when splits > 1 */
+    uint64_t tickets;              /* scratch u32 [rows*heads], zero before the first use (the last split to finish sums the partials in order and zeroes its ticket) */
+    uint32_t rows, heads, kv_heads, dim, vdim, prefix, cache_dt;
+    float scale;
+    uint32_t splits;               /* the causal key range of every query is cut into this many parts, one CTA each (0 / 1 = none) */
+    uint32_t reserved0;
+} uzu_sigmoid_attention_args;
+UZU_API void uzu_sigmoid_attention_encode(uzu_command_buffer* cmd, const uzu_sigmoid_attention_args* args);
 
 /* Generalized delta rule, `rows` tokens of one sequence in token order in one launch, state f32 [heads, dim, dim] (key channel major)
  * carried in `state`:  d = exp(-e^-1/2 * sigmoid(decay_logit + decay_bias)); a = sigmoid(rate_logit + rate_bias);

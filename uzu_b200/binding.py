@@ -136,11 +136,11 @@ DenseLinearArgs = _struct("uzu_dense_linear_args", [
     ("a_z_stride", u64), ("w_z_stride", u64), ("d_z_stride", u64), ("gate", u64), ("workspace", u64),
     ("m", u32), ("n", u32), ("k", u32), ("lda", u32), ("ldd", u32), ("batch", u32),
     ("weights_dt", u32), ("accumulate", u32), ("scale", f32), ("a_op", u32), ("gate_ld", u32), ("pair_rows", u32),
-    ("glu_limit", f32), ("glu_alpha", f32)])
+    ("glu_limit", f32), ("glu_alpha", f32), ("glu_kind", u32), ("reserved0", u32), ("gate_bias", u64), ("col_scale", u64)])
 
 GroupRmsNormArgs = _struct("uzu_group_rms_norm_args", [
     ("input", u64), ("scales", u64), ("output", u64), ("row_indices", u64),
-    ("rows", u32), ("n", u32), ("groups", u32), ("in_stride", u32), ("out_stride", u32), ("epsilon", f32)])
+    ("rows", u32), ("n", u32), ("groups", u32), ("in_stride", u32), ("out_stride", u32), ("epsilon", f32), ("scales2", u64), ("output2", u64)])
 
 TableRouteArgs = _struct("uzu_table_route_args", [
     ("token_ids", u64), ("table", u64), ("group_offsets", u64), ("rows_map", u64), ("pair_pos", u64),
@@ -167,9 +167,29 @@ LatentAttentionArgs = _struct("uzu_latent_attention_args", [
     ("query", u64), ("cache", u64), ("out", u64), ("dynamic_position", u64), ("partials", u64),
     ("rows", u32), ("heads", u32), ("rank", u32), ("rot_dim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32), ("splits", u32)])
 
+TopkRouteArgs = _struct("uzu_topk_route_args", [
+    ("logits", u64), ("bias", u64), ("group_offsets", u64), ("rows_map", u64), ("pair_pos", u64), ("pair_weight", u64),
+    ("rows", u32), ("top", u32), ("experts", u32), ("logits_stride", u32)])
+
+RoutedCombineArgs = _struct("uzu_routed_combine_args", [
+    ("pairs", u64), ("pair_pos", u64), ("pair_weight", u64), ("gate", u64), ("gate_bias", u64), ("col_scale", u64), ("output", u64),
+    ("rows", u32), ("top", u32), ("n", u32), ("gate_ld", u32), ("accumulate", u32), ("weight", f32)])
+
+SigmoidAttentionPrepareArgs = _struct("uzu_sigmoid_attention_prepare_args", [
+    ("q", u64), ("k", u64), ("v", u64), ("q_scales", u64), ("k_scales", u64), ("query", u64), ("keys", u64), ("values", u64),
+    ("dynamic_position", u64),
+    ("rows", u32), ("q_n", u32), ("k_n", u32), ("v_n", u32), ("q_stride", u32), ("k_stride", u32), ("v_stride", u32), ("prefix", u32),
+    ("cache_dt", u32), ("temp_every", u32), ("epsilon", f32), ("temp_coef", f32)])
+
+SigmoidAttentionArgs = _struct("uzu_sigmoid_attention_args", [
+    ("query", u64), ("keys", u64), ("values", u64), ("out", u64), ("dynamic_position", u64),
+    ("dist_r1", u64), ("dist_r2", u64), ("head_bias", u64), ("partials", u64), ("tickets", u64),
+    ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32),
+    ("splits", u32), ("reserved0", u32)])
+
 MAIN_SLOT = 0xFFFFFFFF
 
-ABI_STRUCTS = [DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
+ABI_STRUCTS = [TopkRouteArgs, RoutedCombineArgs, SigmoidAttentionPrepareArgs, SigmoidAttentionArgs, DenseLinearArgs, GroupRmsNormArgs, TableRouteArgs, GeneralDeltaArgs, HeadNormGateArgs, LatentPrepareArgs, LatentAttentionArgs,
                DeltaNetFusedUpdateArgs, QkNormConfig, AttentionPrepareNormArgs, FusedLinearArgs, RingParams, TrieNode, KvCopy, MatmulArgs, NormalizationArgs, QkvNormArgs, AttentionPrepareArgs, AttentionArgs,
                AttentionTwoPass2Args, KvCacheUpdateArgs, GatedActMulArgs, QuantizedEmbeddingLookupArgs, UnifiedSamplingArgs,
                DeltaNetConvUpdateArgs, DeltaNetUpdateArgs, EngineOptions, SamplingMethod, ModelInfo, TpAllGatherArgs]
@@ -200,6 +220,7 @@ uzu_engine_speculation_supported uzu_engine_trie_pass uzu_engine_trie_accept uzu
 uzu_activation_transform_validate uzu_dense_linear_encode uzu_group_rms_norm_encode uzu_embedding_f32_encode uzu_clamped_glu_encode
 uzu_unary_f32_encode uzu_residual_add_encode uzu_logit_cap_f32_encode uzu_table_route_encode uzu_routed_combine_encode
 uzu_general_delta_encode uzu_head_norm_gate_encode uzu_latent_prepare_encode uzu_latent_attention_encode
+uzu_silu_glu_encode uzu_topk_route_encode uzu_routed_combine_gated_encode uzu_sigmoid_attention_prepare_encode uzu_sigmoid_attention_encode
 uzu_engine_slot_acquire uzu_engine_slot_release uzu_engine_forward_rows uzu_engine_debug_layer_outputs uzu_debug_dense_umma_error""".split()
 
 _lib = None
@@ -341,6 +362,11 @@ def load() -> C.CDLL:
         "uzu_residual_add_encode": (None, [vp, u64, u64, u64, u32]),
         "uzu_logit_cap_f32_encode": (None, [vp, u64, u64, u32, f32, u32]),
         "uzu_table_route_encode": (None, [vp, C.POINTER(TableRouteArgs)]),
+        "uzu_topk_route_encode": (None, [vp, C.POINTER(TopkRouteArgs)]),
+        "uzu_routed_combine_gated_encode": (None, [vp, C.POINTER(RoutedCombineArgs)]),
+        "uzu_silu_glu_encode": (None, [vp, u64, u64, u32, u32]),
+        "uzu_sigmoid_attention_prepare_encode": (None, [vp, C.POINTER(SigmoidAttentionPrepareArgs)]),
+        "uzu_sigmoid_attention_encode": (None, [vp, C.POINTER(SigmoidAttentionArgs)]),
         "uzu_routed_combine_encode": (None, [vp, u64, u64, u64, u32, u32, u32, f32, u32]),
         "uzu_general_delta_encode": (None, [vp, C.POINTER(GeneralDeltaArgs)]),
         "uzu_head_norm_gate_encode": (None, [vp, C.POINTER(HeadNormGateArgs)]),

@@ -42,6 +42,7 @@ SOURCES = {
     "residual_f32.cu": [],
     "general_delta.cu": [],
     "latent_attention.cu": [],
+    "sigmoid_attention.cu": [],
     "engine.cu": [],
 }
 

@@ -39,12 +39,21 @@ __device__ __forceinline__ float w_to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float w_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-__device__ __forceinline__ float dense_a(const uzu_dense_linear_args& a, float x) { return a.a_op == 1 ? tanhf(x) : x; }
+__device__ __forceinline__ float dense_a(const uzu_dense_linear_args& a, float x) {
+    if (a.a_op == 1) return tanhf(x);
+    if (a.a_op == 2) { const float r = fmaxf(x, 0.0f); return r * r; }
+    return x;
+}
 
 // `row` is the compact row the value belongs to (the gate is indexed like D)
 __device__ __forceinline__ void dense_store(const uzu_dense_linear_args& a, float* d, uint32_t z, uint32_t row, uint32_t col, float acc) {
     float v = acc * a.scale;
-    if (a.gate) v *= 1.0f / (1.0f + expf(-reinterpret_cast<const float*>(a.gate)[(size_t)row * a.gate_ld + (size_t)z * a.d_z_stride + col]));
+    if (a.gate) {
+        float g = reinterpret_cast<const float*>(a.gate)[(size_t)row * a.gate_ld + (size_t)z * a.d_z_stride + col];
+        if (a.gate_bias) g += reinterpret_cast<const float*>(a.gate_bias)[col];
+        v *= 1.0f / (1.0f + expf(-g));
+    }
+    if (a.col_scale) v *= reinterpret_cast<const float*>(a.col_scale)[col];
     if (a.bias && z == 0) v += reinterpret_cast<const float*>(a.bias)[col];
     if (a.accumulate) v += *d;
     *d = v;
@@ -203,7 +212,7 @@ __global__ void __launch_bounds__(256, RMAX == 1 ? 4 : 2) dense_rows_kernel(cons
     }
     auto finish = [&](uint32_t r, float s, float s2) {
         float* d = reinterpret_cast<float*>(a.d) + (size_t)z * a.d_z_stride + (size_t)(R.begin + r) * a.ldd + col;
-        if constexpr (PAIR) *d = clamped_glu_value(s, s2, a.glu_limit, a.glu_alpha);
+        if constexpr (PAIR) *d = a.glu_kind == 1 ? s * (1.0f / (1.0f + expf(-s))) * s2 : clamped_glu_value(s, s2, a.glu_limit, a.glu_alpha);
         else dense_store(a, d, z, R.begin + r, col, s);
     };
 #pragma unroll
@@ -549,7 +558,7 @@ extern "C" void uzu_dense_linear_encode(uzu_command_buffer* cmd, const uzu_dense
         cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: null operand / bad dtype / bad batch");
         return;
     }
-    if (a.a_op > 1 || (a.pair_rows && (a.gate || a.bias || a.accumulate))) {
+    if (a.a_op > 2 || a.glu_kind > 1 || (a.gate_bias && !a.gate) || (a.pair_rows && (a.gate || a.bias || a.accumulate || a.col_scale))) {
         cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "dense_linear: unknown A operation, or a paired epilogue combined with gate / bias / accumulate");
         return;
     }

@@ -21,6 +21,8 @@ struct DenseUmmaParams {
     const __nv_bfloat16* w;    // [n, k]
     float* d;                  // [m, ldd]
     const float* gate;         // optional [m, gate_ld]
+    const float* gate_bias;    // optional [n], added to the gate
+    const float* col_scale;    // optional [n]
     uint32_t m, n, k, ldd, gate_ld, accumulate;
     float scale;
     uint32_t desc_hi, desc_lbo, k_step, idesc;
@@ -169,7 +171,8 @@ __global__ void __launch_bounds__(DU_NP + 32, 1) dense_umma_kernel(const DenseUm
                 for (int j = 0; j < 32; ++j) {
                     if (col0 + (uint32_t)j < p.n) {
                         float val = __uint_as_float(v[j]) * p.scale;
-                        if (gate) val *= 1.0f / (1.0f + expf(-gate[j]));
+                        if (gate) val *= 1.0f / (1.0f + expf(-(gate[j] + (p.gate_bias ? p.gate_bias[col0 + j] : 0.0f))));
+                        if (p.col_scale) val *= p.col_scale[col0 + j];
                         if (p.accumulate) val += out[j];
                         out[j] = val;
                     }
@@ -219,6 +222,10 @@ __global__ void dense_cast_bf16_kernel(const float* a, uint32_t lda, __nv_bfloat
     const size_t r = idx / k, c = idx % k;                       // k is a multiple of 64: the four elements share a row
     float4 v = *reinterpret_cast<const float4*>(a + r * lda + c);
     if (a_op == 1) { v.x = tanhf(v.x); v.y = tanhf(v.y); v.z = tanhf(v.z); v.w = tanhf(v.w); }
+    if (a_op == 2) {
+        v.x = fmaxf(v.x, 0.0f); v.y = fmaxf(v.y, 0.0f); v.z = fmaxf(v.z, 0.0f); v.w = fmaxf(v.w, 0.0f);
+        v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;
+    }
     const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t*>(&lo);
@@ -245,6 +252,8 @@ void encode_dense_umma(uzu_command_buffer* cmd, const uzu_dense_linear_args& a) 
     p.w = (const __nv_bfloat16*)a.w;
     p.d = (float*)a.d;
     p.gate = (const float*)a.gate;
+    p.gate_bias = (const float*)a.gate_bias;
+    p.col_scale = (const float*)a.col_scale;
     p.m = a.m; p.n = a.n; p.k = a.k; p.ldd = a.ldd; p.gate_ld = a.gate_ld; p.accumulate = a.accumulate;
     p.scale = a.scale;
     // shared-memory matrix descriptor: start address >> 4 @ [0,14), LBO >> 4 @ [16,30), SBO >> 4 @ [32,46), version 1 @ [46,48), layout

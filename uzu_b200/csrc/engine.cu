@@ -344,15 +344,34 @@ struct LatentAttentionLayer {   // latent attention: normed query latent, shared
     int rope_index = -1;
 };
 
-struct GatedMlp {               // clamped gated unit; dense, or experts picked per token id from a table
-    enum Kind { None, Dense, TableExperts } kind = None;
-    DenseMatrix gate_up /* experts x [2f, W]: gate rows then up rows */, down /* experts x [W, f] */;
-    Buf table;                  // i32 [vocab, top]
+struct SigmoidAttentionLayer {  // sigmoid attention: whole-projection q / k norms, distance bias, query temperature, optional borrowed cache
+    DenseMatrix in;             // rows [query | key | value | sublayer gate]; a layer that borrows its cache has no key / value rows
+    DenseMatrix out;
+    Buf q_norm, k_norm;         // f32 [heads*dim], [kv_heads*dim]
+    Buf dist_r1, dist_r2, head_bias;   // f32 [heads]
+    uint32_t heads = 0, kv_heads = 0, dim = 0, vdim = 0, temp_every = 0;
+    int kv_from = -1;           // >= 0: this layer reads the cache of that (earlier) layer and keeps none
+    float scale = 1.0f, temp_coef = 0.0f;
+};
+
+struct SublayerGate {           // y * scale[c] * sigmoid(gate_logit[c] + bias[c]); the gate logits are extra rows of the sublayer's stacked input projection
+    bool present = false;
+    Buf scale, bias;            // f32 [width]
+    uint32_t offset = 0;        // first gate column of the stacked projection's output
+};
+
+struct GatedMlp {               // feed-forward: dense or routed experts; the unit is a clamped gated one, silu(g) * u, or relu(u)^2 (no gate rows)
+    enum Kind { None, Dense, TableExperts, RoutedExperts } kind = None;
+    enum Unit { ClampedGlu, SiluGlu, ReluSquared } unit = ClampedGlu;
+    DenseMatrix gate_up /* experts x [2f, W]: gate rows then up rows; ReluSquared: [f (+ W gate logits), W] */, down /* experts x [W, f] */;
+    DenseMatrix router;         // RoutedExperts: rows [router logits | sublayer gate]
+    Buf table;                  // TableExperts: i32 [vocab, top]
+    Buf router_bias;            // RoutedExperts: f32 [experts]
     uint32_t f = 0, experts = 1, top = 1;
     float limit = 0.0f;
 };
 
-enum MixerKind : uint32_t { MixAttention = 0, MixDeltaNet = 1, MixGeneralDelta = 2, MixLatentAttention = 3 };
+enum MixerKind : uint32_t { MixAttention = 0, MixDeltaNet = 1, MixGeneralDelta = 2, MixLatentAttention = 3, MixSigmoidAttention = 4 };
 
 struct Layer {
     bool is_attention = true;   // the mixer keeps a per-token cache whose length advances with the context (MixAttention, MixLatentAttention)
@@ -362,6 +381,8 @@ struct Layer {
     DeltaNetLayer dn;
     GeneralDeltaLayer gd;
     LatentAttentionLayer la;
+    SigmoidAttentionLayer sa;
+    SublayerGate mix_gate, mlp_gate;
     GatedMlp gmlp;
     Linear up, down;
     uint32_t hidden_dim = 0;
@@ -448,6 +469,7 @@ struct uzu_engine {
     DenseMatrix pb_embed, pb_head;
     Buf pb_final_norm;
     struct PbScratch {
+        Buf normed2, proj2, pair_weight, attn_tickets;   // second normed copy, the feed-forward's router / gate logits, router weights, split tickets
         Buf resid, normed, operand_bf16, proj, lat, wide, lat_wide, query, attn_partial, mixed, gated_mix, gate_up, act, pair_out, group_offsets, rows_map, pair_pos,
             normed_rows, logits_f32, layer_dump;
         uint32_t dump_rows = 0;
@@ -704,6 +726,7 @@ static void rope_tables(const RopeCfg& c, uint32_t count, float* cosines, float*
 }
 
 static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std::string& dir);
+static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string& dir);
 static void load_language_model_config(uzu_engine* e, const Json& cfg, const std::string& dir);
 
 // Model registry: config.json names its family, either by the reference's type tag or by an "architecture" string.
@@ -715,6 +738,7 @@ struct ModelFamily {
 static const ModelFamily kModelFamilies[] = {
     {"LanguageModelConfig", [](const Json& c) { const Json* t = c.get("type"); return t && t->str == "LanguageModelConfig"; }, load_language_model_config},
     {"Punilix", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Punilix"; }, load_parallel_block_model},
+    {"Gamanex", [](const Json& c) { const Json* a = c.get("architecture"); return a && a->str == "Gamanex"; }, load_gamanex_model},
 };
 
 static void load_model(uzu_engine* e, const std::string& dir) {
@@ -911,6 +935,14 @@ static void alloc_layer_state(uzu_engine* e, const Layer& L, LayerState& S, uint
         case MixLatentAttention: {   // one row per token: [latent | rotated key part], shared by all heads; no separate values
             S.row_bytes = (size_t)(L.la.rank + L.la.rot_dim) * storage_size(e->store_dt);
             paged(S.k_sparse, S.k_dense, S.keys, (size_t)rows_total * S.row_bytes);
+            break;
+        }
+        case MixSigmoidAttention: {  // keys [kv_heads*dim] and values [kv_heads*vdim] per token, unless the layer reads another layer's cache
+            if (L.sa.kv_from >= 0) break;
+            const size_t kb = (size_t)L.sa.kv_heads * L.sa.dim * storage_size(e->store_dt), vb = (size_t)L.sa.kv_heads * L.sa.vdim * storage_size(e->store_dt);
+            S.row_bytes = std::max(kb, vb);     // both buffers reserve the larger row's range: their pages are mapped by one page list
+            paged(S.k_sparse, S.k_dense, S.keys, (size_t)rows_total * S.row_bytes);
+            paged(S.v_sparse, S.v_dense, S.values, (size_t)rows_total * S.row_bytes);
             break;
         }
         case MixDeltaNet: {

@@ -1,12 +1,15 @@
-// Parallel-block family (Punilix) inside the host engine: configuration, weights, scratch and the encoding of one pass. Included by
-// engine.cu; the pass driver, the state / cache manager, sampling, CUDA-graph decode and the sequence slots are the engine's own.
+// Parallel-block families (Punilix, Gamanex) inside the host engine: configuration, weights, scratch and the encoding of one pass.
+// Included by engine.cu; the pass driver, the state / cache manager, sampling, CUDA-graph decode and the sequence slots are the engine's own.
 //
 //   x = embed[token]                                                      (f32 residual stream)
-//   per layer:  h = group_rms(x);  x <- x + mixer(h) + mlp(h)             (one norm feeds both sublayers)
-//   logits = cap * tanh(head . group_rms(x) / cap)
+//   Punilix layer:  h = group_rms(x);  x <- x + mixer(h) + mlp(h)         (one norm feeds both sublayers)
+//   Gamanex layer:  h1 = rms(x) n1, h2 = rms(x) n2;  x <- x + ls1 sigmoid(G1 h1 + b1) mixer(h1) + ls2 sigmoid(G2 h2 + b2) mlp(h2)
+//   logits = cap * tanh(head . group_rms(x) / cap)   |   logit_scale * head . rms(x)
 //
-// config.json: "architecture", "width", "vocab", "norm": {"eps", "groups"}, "logit_softcap", "layers": [{"type", "mixer": {...}, "mlp"}].
-// Tensors: embed, head, final.norm, l<i>.norm1, l<i>.mix.*, l<i>.mlp.* (bf16 or f32 floats, i32 tables); linear weights are [out, in].
+// Both are described by the same Layer fields (a second norm, sublayer gates and a logit scale are optional parts) and encoded by the same
+// loop; a family is a config reader that fills them.
+// config.json: "architecture", "width", "vocab", "norm": {"eps", "groups"}, "logit_softcap" | "logit_scale", "layers": [{"type", "mixer": {...}, "mlp"}].
+// Tensors: embed, head, final.norm, l<i>.norm1 (norm2), l<i>.mix.*, l<i>.mlp.* (bf16 or f32 floats, i32 tables); linear weights are [out, in].
 // Weights are assembled on the host at load: projections that read the same input are stacked into one matrix, per-head key
 // up-projections are transposed for the absorbed form, expert matrices lie back to back. Storage is bf16, or f32 when the engine was
 // created with storage_f32 (then every product is a plain f32 multiply-add).
@@ -253,6 +256,152 @@ static void load_parallel_block_model(uzu_engine* e, const Json& cfg, const std:
     e->info.state_bytes_per_token = stb;
 }
 
+// Gamanex: sigmoid attention mixers (optionally reading an earlier layer's keys and values), relu^2 dense or routed silu-gated expert
+// feed-forwards, two norms of the same input per layer, every sublayer's result times a per-channel scale and a sigmoid gate of its input.
+// config.json: "width", "vocab", "norm": {"eps"}, "logit_scale", "layers": [{"type": "attention", "mixer": {"heads", "kv_heads", "dim",
+// "vdim", "scale", "q_temp": {"coef", "every"}, "kv_from"}, "mlp": null | {"kind": "dense", "ff"} | {"kind": "moe", "expert": {"ff"},
+// "router": {"experts", "top"}}}]. Tensors: l<i>.norm1/2, l<i>.mix.{q,k,v,o,q.norm,k.norm,r1,r2,pb}, l<i>.mlp.{up,down} or
+// l<i>.mlp.{router,router.b,e<x>.{gate,up,down}}, l<i>.ls1/2, l<i>.rg1/2 (+ .b).
+static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string& dir) {
+    if (e->opts.tp_size > 1) throw std::runtime_error("tensor parallelism is not built for the parallel-block families");
+    e->parallel_block = true;
+    e->store_dt = e->opts.storage_f32 ? UZU_DT_F32 : UZU_DT_BF16;
+    const uint32_t W = e->model_dim = cfg_u32(cfg, "width");
+    const uint32_t V = e->vocab = cfg_u32(cfg, "vocab");
+    e->norm_eps = (float)cfg.at("norm").at("eps").number();
+    e->norm_groups = 1;
+    if (const Json* ls = cfg.get("logit_scale")) {
+        if (!ls->is_null()) { e->has_logit_scale = true; e->logit_scale = (float)ls->number(); }
+    }
+    ParameterLoader pl(dir + "/model.safetensors");
+    e->pb_embed = upload_matrix(e, read_floats(pl, "embed", {V, W}).v, V, W);
+    e->pb_head = upload_matrix(e, read_floats(pl, "head", {V, W}).v, V, W);
+    e->pb_final_norm = upload_f32(e, read_floats(pl, "final.norm", {W}).v);
+    uint64_t wbytes = e->pb_head.bytes, kvb = 0;
+    uint32_t n_cache = 0;
+    const auto& lcs = cfg.at("layers").arr;
+    e->layers.resize(lcs.size());
+    auto sublayer_gate = [&](SublayerGate& g, std::vector<float>& stacked, uint32_t rows_before, const std::string& p, const char* scale, const char* gate) {
+        g.present = true;
+        g.offset = rows_before;
+        append(stacked, read_floats(pl, p + gate, {W, W}));
+        g.bias = upload_f32(e, read_floats(pl, p + gate + ".b", {W}).v);
+        g.scale = upload_f32(e, read_floats(pl, p + scale, {W}).v);
+    };
+    for (size_t i = 0; i < lcs.size(); ++i) {
+        const Json& lc = lcs[i];
+        Layer& L = e->layers[i];
+        const std::string p = "l" + std::to_string(i) + ".";
+        L.pre_mixer.present = true;
+        L.pre_mixer.n = W;
+        L.pre_mixer.cfg.epsilon = e->norm_eps;
+        L.pre_mixer.scales = upload_f32(e, read_floats(pl, p + "norm1", {W}).v);
+        const std::string type = lc.at("type").str;
+        if (type != "attention") throw std::runtime_error("layer type '" + type + "' is not known to the Gamanex family");
+        const Json& mc = lc.at("mixer");
+        L.kind = MixSigmoidAttention;
+        L.is_attention = true;
+        SigmoidAttentionLayer& A = L.sa;
+        A.heads = cfg_u32(mc, "heads");
+        A.kv_heads = cfg_u32(mc, "kv_heads");
+        A.dim = cfg_u32(mc, "dim");
+        A.vdim = cfg_u32(mc, "vdim");
+        A.scale = (float)mc.at("scale").number();
+        if (A.heads == 0 || A.kv_heads == 0 || A.heads % A.kv_heads || A.dim == 0 || A.vdim == 0 || A.dim > 512 || A.vdim > 512)
+            throw std::runtime_error(p + "mix: kv_heads must divide heads, head sizes must be in 1..512");
+        if (const Json* qt = mc.get("q_temp")) {
+            if (!qt->is_null()) {
+                A.temp_coef = (float)qt->at("coef").number();
+                A.temp_every = cfg_u32(*qt, "every");
+                if (A.temp_every == 0) throw std::runtime_error(p + "mix: q_temp.every must be positive");
+            }
+        }
+        if (const Json* kf = mc.get("kv_from")) {
+            if (!kf->is_null()) {
+                A.kv_from = (int)cfg_u32(mc, "kv_from");
+                if ((size_t)A.kv_from >= i) throw std::runtime_error(p + "mix: kv_from must name an earlier layer");
+                const SigmoidAttentionLayer& src = e->layers[A.kv_from].sa;
+                if (e->layers[A.kv_from].kind != MixSigmoidAttention || src.kv_from >= 0 || src.kv_heads != A.kv_heads || src.dim != A.dim || src.vdim != A.vdim)
+                    throw std::runtime_error(p + "mix: kv_from must name a layer that keeps its own keys and values with the same head count and sizes");
+            }
+        }
+        const uint32_t qn = A.heads * A.dim, kn = A.kv_heads * A.dim, vn = A.kv_heads * A.vdim;
+        std::vector<float> in;
+        append(in, read_floats(pl, p + "mix.q", {qn, W}));
+        uint32_t rows = qn;
+        A.q_norm = upload_f32(e, read_floats(pl, p + "mix.q.norm", {qn}).v);
+        if (A.kv_from < 0) {
+            append(in, read_floats(pl, p + "mix.k", {kn, W}));
+            append(in, read_floats(pl, p + "mix.v", {vn, W}));
+            A.k_norm = upload_f32(e, read_floats(pl, p + "mix.k.norm", {kn}).v);
+            rows += kn + vn;
+            kvb += (uint64_t)(kn + vn) * storage_size(e->store_dt);
+            n_cache++;
+        }
+        sublayer_gate(L.mix_gate, in, rows, p, "ls1", "rg1");
+        A.in = upload_matrix(e, in, rows + W, W);
+        A.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
+        A.dist_r1 = upload_f32(e, read_floats(pl, p + "mix.r1", {A.heads}).v);
+        A.dist_r2 = upload_f32(e, read_floats(pl, p + "mix.r2", {A.heads}).v);
+        A.head_bias = upload_f32(e, read_floats(pl, p + "mix.pb", {A.heads}).v);
+        wbytes += A.in.bytes + A.out.bytes;
+        GatedMlp& M = L.gmlp;
+        const Json* ml = lc.get("mlp");
+        if (!ml || ml->is_null()) continue;
+        L.pre_mlp.present = true;
+        L.pre_mlp.n = W;
+        L.pre_mlp.cfg.epsilon = e->norm_eps;
+        L.pre_mlp.scales = upload_f32(e, read_floats(pl, p + "norm2", {W}).v);
+        const std::string kind = ml->at("kind").str;
+        if (kind == "dense") {
+            M.kind = GatedMlp::Dense;
+            M.unit = GatedMlp::ReluSquared;
+            M.f = cfg_u32(*ml, "ff");
+            if (M.f == 0) throw std::runtime_error(p + "mlp: ff must be positive");
+            std::vector<float> up;
+            append(up, read_floats(pl, p + "mlp.up", {M.f, W}));
+            sublayer_gate(L.mlp_gate, up, M.f, p, "ls2", "rg2");
+            M.gate_up = upload_matrix(e, up, M.f + W, W);
+            M.down = upload_matrix(e, read_floats(pl, p + "mlp.down", {W, M.f}).v, W, M.f);
+            wbytes += M.gate_up.bytes + M.down.bytes;
+        } else if (kind == "moe") {
+            M.kind = GatedMlp::RoutedExperts;
+            M.unit = GatedMlp::SiluGlu;
+            M.f = cfg_u32(ml->at("expert"), "ff");
+            M.experts = cfg_u32(ml->at("router"), "experts");
+            M.top = cfg_u32(ml->at("router"), "top");
+            if (M.f == 0 || M.experts == 0 || M.top == 0 || M.top > M.experts || M.experts > 8192 || (uint64_t)MAX_ROWS * M.top * 2 > 40000)
+                throw std::runtime_error(p + "mlp: bad expert / top counts");
+            std::vector<float> ro, gu, dn;
+            append(ro, read_floats(pl, p + "mlp.router", {M.experts, W}));
+            sublayer_gate(L.mlp_gate, ro, M.experts, p, "ls2", "rg2");
+            M.router = upload_matrix(e, ro, M.experts + W, W);
+            M.router_bias = upload_f32(e, read_floats(pl, p + "mlp.router.b", {M.experts}).v);
+            for (uint32_t x = 0; x < M.experts; ++x) {
+                const std::string q = p + "mlp.e" + std::to_string(x) + ".";
+                append(gu, read_floats(pl, q + "gate", {M.f, W}));
+                append(gu, read_floats(pl, q + "up", {M.f, W}));
+                append(dn, read_floats(pl, q + "down", {W, M.f}));
+            }
+            M.gate_up = upload_matrix(e, gu, 2 * M.f, W, M.experts);
+            M.down = upload_matrix(e, dn, W, M.f, M.experts);
+            wbytes += M.router.bytes + (M.gate_up.bytes + M.down.bytes) / M.experts * M.top;
+        } else {
+            throw std::runtime_error("mlp kind '" + kind + "' is not known to the Gamanex family");
+        }
+    }
+    pl.assert_all_validated();
+    e->info.model_dim = W;
+    e->info.hidden_dim = 0;
+    e->info.vocab_size = V;
+    e->info.num_layers = (uint32_t)e->layers.size();
+    e->info.num_attention_layers = n_cache;
+    e->info.num_delta_net_layers = 0;
+    e->info.weight_bytes_per_token = wbytes;
+    e->info.kv_bytes_per_token_per_ctx = kvb;
+    e->info.state_bytes_per_token = 0;
+}
+
 constexpr uint32_t kSplitRows = 256;   // query rows x key splits of one latent-attention launch that leaves partial softmax states
 
 // scratch of the family: f32 row blocks sized by the widest layer
@@ -260,8 +409,19 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     if (!e->parallel_block) return;
     const uint32_t W = e->model_dim;
     uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1, kmax = e->model_dim;
+    uint32_t proj2 = 1, tickets = 1;
+    bool second_norm = false;
     for (const Layer& L : e->layers) {
-        if (L.kind == MixGeneralDelta) {
+        second_norm = second_norm || L.pre_mlp.present;
+        if (L.kind == MixSigmoidAttention) {
+            const SigmoidAttentionLayer& A = L.sa;
+            proj = std::max(proj, A.in.rows);
+            query = std::max(query, A.heads * A.dim);
+            mixed = std::max(mixed, A.heads * A.vdim);
+            partial = std::max(partial, A.heads * A.vdim);
+            tickets = std::max(tickets, A.heads);
+            kmax = std::max(kmax, A.heads * A.vdim);
+        } else if (L.kind == MixGeneralDelta) {
             const uint32_t HD = L.gd.heads * L.gd.dim;
             proj = std::max(proj, L.gd.in.rows);
             lat = std::max(lat, L.gd.decay_rank);
@@ -280,6 +440,8 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             partial = std::max(partial, A.heads * (A.rank + 2));
             kmax = std::max({kmax, A.q_rank, A.heads * A.vdim});
         }
+        if (L.gmlp.kind == GatedMlp::RoutedExperts) proj2 = std::max(proj2, L.gmlp.router.rows);
+        if (L.gmlp.unit == GatedMlp::ReluSquared) proj2 = std::max(proj2, L.gmlp.gate_up.rows);
         if (L.gmlp.kind != GatedMlp::None) {
             gu = std::max(gu, 2 * L.gmlp.f);
             act = std::max(act, L.gmlp.f);
@@ -293,6 +455,11 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     auto& P = e->pb;
     P.resid = dev(R * W * 4);
     P.normed = dev(R * W * 4);
+    if (second_norm) P.normed2 = dev(R * W * 4);
+    P.proj2 = dev(R * proj2 * 4);
+    P.pair_weight = dev(R * top * 4);
+    P.attn_tickets = dev((size_t)kSplitRows * tickets * 4);
+    cudaMemset((void*)P.attn_tickets.ptr(), 0, (size_t)kSplitRows * tickets * 4);
     P.operand_bf16 = dev(R * kmax * 2);     // bf16 copy of a prompt pass's activation rows for the tensor-memory products
     P.proj = dev(R * proj * 4);
     P.lat = dev(R * lat * 4);
@@ -327,11 +494,54 @@ static void encode_dense(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatr
     uzu_dense_linear_encode(cmd, &x);
 }
 
-// x += A . W^T: the sublayers' output projections add straight into the residual stream
-static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatrix& w, uint64_t a, uint32_t lda, uint32_t rows) {
+// x += A . W^T: the sublayers' output projections add straight into the residual stream. With a sublayer gate the product is first
+// multiplied by scale[c] * sigmoid(logits[row, c] + bias[c]); the logits are columns [offset, offset + width) of a [rows, gate_ld] block.
+static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const DenseMatrix& w, uint64_t a, uint32_t lda, uint32_t rows,
+                                 const SublayerGate* g = nullptr, uint64_t gate_block = 0, uint32_t gate_ld = 0, uint32_t a_op = 0) {
     uzu_dense_linear_args x = dense_args(e, w, a, rows, e->pb.resid.ptr());
-    x.lda = lda; x.accumulate = 1;
+    x.lda = lda; x.accumulate = 1; x.a_op = a_op;
+    if (g && g->present) {
+        x.gate = gate_block + (uint64_t)g->offset * 4; x.gate_ld = gate_ld;
+        x.gate_bias = g->bias.ptr(); x.col_scale = g->scale.ptr();
+    }
     uzu_dense_linear_encode(cmd, &x);
+}
+
+// h [m, W] -> sigmoid attention over the layer's own cache or the cache of the layer it borrows from; the output projection adds into the
+// residual stream through the sublayer gate
+static void encode_sigmoid_attention(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, LayerState& own, const PassCtx& pc) {
+    const SigmoidAttentionLayer& A = L.sa;
+    auto& P = e->pb;
+    LayerState& C = A.kv_from >= 0 ? e->state[A.kv_from] : own;      // the lender ran earlier in this pass: its rows of the pass are in place
+    const uint32_t m = pc.m, ld = A.in.rows, qn = A.heads * A.dim, kn = A.kv_heads * A.dim, vn = A.kv_heads * A.vdim;
+    const uint64_t dyn = pc.dynamic ? e->decode_state.ptr() : 0;
+    encode_dense(e, cmd, A.in, P.normed.ptr(), e->model_dim, m, P.proj.ptr());            // [query | key | value | gate logits]
+    uzu_sigmoid_attention_prepare_args pa{};
+    pa.q = P.proj.ptr(); pa.q_scales = A.q_norm.ptr(); pa.query = P.query.ptr();
+    if (A.kv_from < 0) {
+        pa.k = P.proj.ptr() + (uint64_t)qn * 4; pa.v = P.proj.ptr() + (uint64_t)(qn + kn) * 4; pa.k_scales = A.k_norm.ptr();
+        pa.keys = C.keys; pa.values = C.values;
+    }
+    pa.dynamic_position = dyn;
+    pa.rows = m; pa.q_n = qn; pa.k_n = kn; pa.v_n = vn; pa.q_stride = pa.k_stride = pa.v_stride = ld;
+    pa.prefix = C.length; pa.cache_dt = e->store_dt; pa.temp_every = A.temp_every; pa.temp_coef = A.temp_coef; pa.epsilon = e->norm_eps;
+    uzu_sigmoid_attention_prepare_encode(cmd, &pa);
+    uzu_sigmoid_attention_args aa{};
+    aa.query = P.query.ptr(); aa.keys = C.keys; aa.values = C.values; aa.out = P.mixed.ptr(); aa.dynamic_position = dyn;
+    aa.dist_r1 = A.dist_r1.ptr(); aa.dist_r2 = A.dist_r2.ptr(); aa.head_bias = A.head_bias.ptr();
+    aa.rows = m; aa.heads = A.heads; aa.kv_heads = A.kv_heads; aa.dim = A.dim; aa.vdim = A.vdim; aa.prefix = C.length; aa.cache_dt = e->store_dt;
+    aa.scale = A.scale;
+    {   // few query rows (decode, short portions): cut the keys so that about two CTAs per SM run (the captured step sizes the cut for the
+        // largest context its graph serves)
+        const uint32_t bound = pc.dynamic ? attention_bucket(C.length + m) : C.length + m;
+        const uint32_t tiles = (bound + 31) / 32;
+        const uint32_t want = std::max(1u, 2u * (uint32_t)e->ctx->sm_count / std::max(1u, m * A.heads));
+        aa.splits = std::min({tiles, want, kSplitRows / std::max(1u, m), 64u});
+        aa.partials = P.attn_partial.ptr(); aa.tickets = P.attn_tickets.ptr();
+        if (aa.splits < 2 || m > kSplitRows) aa.splits = 1;
+    }
+    uzu_sigmoid_attention_encode(cmd, &aa);
+    encode_into_residual(e, cmd, A.out, P.mixed.ptr(), A.heads * A.vdim, m, &L.mix_gate, P.proj.ptr(), ld);
 }
 
 // h [m, W] -> the mixer's output is added to the residual stream
@@ -416,47 +626,77 @@ static void encode_latent_attention(uzu_engine* e, uzu_command_buffer* cmd, cons
 
 // h [m, W] -> the feed-forward output is added to the residual stream. Passes of at most 8 rows (decode) form gate and up in one launch
 // that stores the gated unit; longer passes run the stacked [gate | up] product and the unit as two kernels.
-static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, const PassCtx& pc) {
+// `h` is the sublayer's normed input [m, W]. Units: the clamped gated unit, silu(g) * u, or relu(u)^2 (no gate rows; the square is
+// applied as the down projection reads its operand). A sublayer gate's logits come out of the first product of the sublayer (extra rows
+// of the up matrix or of the router) and are applied where the result enters the residual stream.
+static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer& L, const PassCtx& pc, uint64_t h) {
     const GatedMlp& M = L.gmlp;
     auto& P = e->pb;
     const uint32_t m = pc.m, W = e->model_dim;
     constexpr float kGateSlope = 1.702f;
     const bool paired = m <= 8;
     auto gate_up_args = [&]() {
-        uzu_dense_linear_args up = dense_args(e, M.gate_up, P.normed.ptr(), m, paired ? P.act.ptr() : P.gate_up.ptr());
+        uzu_dense_linear_args up = dense_args(e, M.gate_up, h, m, paired ? P.act.ptr() : P.gate_up.ptr());
         up.lda = W;
-        if (paired) { up.n = M.f; up.ldd = M.f; up.pair_rows = M.f; up.glu_limit = M.limit; up.glu_alpha = kGateSlope; }
+        if (paired) { up.n = M.f; up.ldd = M.f; up.pair_rows = M.f; up.glu_limit = M.limit; up.glu_alpha = kGateSlope; up.glu_kind = M.unit == GatedMlp::SiluGlu ? 1 : 0; }
         return up;
     };
+    auto unit = [&](uint32_t rows) {
+        if (M.unit == GatedMlp::SiluGlu) uzu_silu_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), rows, M.f);
+        else uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), rows, M.f, M.limit, kGateSlope);
+    };
+    if (M.kind == GatedMlp::Dense && M.unit == GatedMlp::ReluSquared) {
+        const uint32_t ld = M.gate_up.rows;                                       // [up | gate logits]
+        encode_dense(e, cmd, M.gate_up, h, W, m, P.proj2.ptr());
+        encode_into_residual(e, cmd, M.down, P.proj2.ptr(), ld, m, &L.mlp_gate, P.proj2.ptr(), ld, 2);
+        return;
+    }
     if (M.kind == GatedMlp::Dense) {
         uzu_dense_linear_args up = gate_up_args();
         uzu_dense_linear_encode(cmd, &up);
-        if (!paired) uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m, M.f, M.limit, kGateSlope);
+        if (!paired) unit(m);
         encode_into_residual(e, cmd, M.down, P.act.ptr(), M.f, m);
         return;
     }
-    // table-routed experts: expert-sorted (token, slot) pairs, grouped products over the pairs, weighted combine per token
-    uzu_table_route_args ra{};
-    ra.token_ids = e->token_ids.ptr(); ra.table = M.table.ptr(); ra.group_offsets = P.group_offsets.ptr(); ra.rows_map = P.rows_map.ptr();
-    ra.pair_pos = P.pair_pos.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts; ra.vocab = e->vocab;
-    uzu_table_route_encode(cmd, &ra);
+    // routed experts: expert-sorted (token, slot) pairs, grouped products over the pairs, weighted combine per token
+    if (M.kind == GatedMlp::RoutedExperts) {
+        encode_dense(e, cmd, M.router, h, W, m, P.proj2.ptr());                   // [router logits | gate logits]
+        uzu_topk_route_args ra{};
+        ra.logits = P.proj2.ptr(); ra.bias = M.router_bias.ptr(); ra.group_offsets = P.group_offsets.ptr(); ra.rows_map = P.rows_map.ptr();
+        ra.pair_pos = P.pair_pos.ptr(); ra.pair_weight = P.pair_weight.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts;
+        ra.logits_stride = M.router.rows;
+        uzu_topk_route_encode(cmd, &ra);
+    } else {
+        uzu_table_route_args ra{};
+        ra.token_ids = e->token_ids.ptr(); ra.table = M.table.ptr(); ra.group_offsets = P.group_offsets.ptr(); ra.rows_map = P.rows_map.ptr();
+        ra.pair_pos = P.pair_pos.ptr(); ra.rows = m; ra.top = M.top; ra.experts = M.experts; ra.vocab = e->vocab;
+        uzu_table_route_encode(cmd, &ra);
+    }
     uzu_dense_linear_args up = gate_up_args();
     up.batch = M.experts; up.w_z_stride = M.gate_up.stride();
     up.group_offsets = P.group_offsets.ptr(); up.rows_map = P.rows_map.ptr();
     uzu_dense_linear_encode(cmd, &up);
-    if (!paired) uzu_clamped_glu_encode(cmd, P.gate_up.ptr(), P.act.ptr(), m * M.top, M.f, M.limit, kGateSlope);
+    if (!paired) unit(m * M.top);
     uzu_dense_linear_args dn = dense_args(e, M.down, P.act.ptr(), m, P.pair_out.ptr());
     dn.lda = M.f; dn.batch = M.experts; dn.w_z_stride = M.down.stride();
     dn.group_offsets = P.group_offsets.ptr();
     uzu_dense_linear_encode(cmd, &dn);
-    uzu_routed_combine_encode(cmd, P.pair_out.ptr(), P.pair_pos.ptr(), P.resid.ptr(), m, M.top, W, 1.0f / (float)M.top, 1);
+    uzu_routed_combine_args ca{};
+    ca.pairs = P.pair_out.ptr(); ca.pair_pos = P.pair_pos.ptr(); ca.output = P.resid.ptr(); ca.rows = m; ca.top = M.top; ca.n = W; ca.accumulate = 1;
+    if (M.kind == GatedMlp::RoutedExperts) { ca.pair_weight = P.pair_weight.ptr(); ca.weight = 1.0f; }
+    else ca.weight = 1.0f / (float)M.top;
+    if (L.mlp_gate.present) {
+        ca.gate = P.proj2.ptr() + (uint64_t)L.mlp_gate.offset * 4; ca.gate_ld = M.router.rows;
+        ca.gate_bias = L.mlp_gate.bias.ptr(); ca.col_scale = L.mlp_gate.scale.ptr();
+    }
+    uzu_routed_combine_gated_encode(cmd, &ca);
 }
 
 static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd, const PassCtx& pc, uint32_t row_begin, uint32_t row_end) {
     const uint32_t m = pc.m, W = e->model_dim;
     auto& P = e->pb;
     if (pc.trie) {
-        cmd->record_error(UZU_ERROR_UNSUPPORTED, "speculation passes are not built for the parallel-block family");
+        cmd->record_error(UZU_ERROR_UNSUPPORTED, "speculation passes are not built for the parallel-block families");
         return;
     }
     uzu_embedding_f32_encode(cmd, e->token_ids.ptr(), e->pb_embed.w.ptr(), e->store_dt, P.resid.ptr(), m, e->vocab, W);
@@ -467,10 +707,13 @@ static void encode_parallel_block_decoder(uzu_engine* e, uzu_command_buffer* cmd
         uzu_group_rms_norm_args na{};
         na.input = P.resid.ptr(); na.scales = L.pre_mixer.scales.ptr(); na.output = P.normed.ptr();
         na.rows = m; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
+        const bool second = L.pre_mlp.present && L.gmlp.kind != GatedMlp::None;      // the feed-forward norms the same x with its own weights
+        if (second) { na.scales2 = L.pre_mlp.scales.ptr(); na.output2 = P.normed2.ptr(); }
         uzu_group_rms_norm_encode(cmd, &na);
         if (L.kind == MixGeneralDelta) encode_general_delta(e, cmd, L, S, pc);
+        else if (L.kind == MixSigmoidAttention) encode_sigmoid_attention(e, cmd, L, S, pc);
         else encode_latent_attention(e, cmd, L, S, pc);
-        if (L.gmlp.kind != GatedMlp::None) encode_gated_mlp(e, cmd, L, pc);
+        if (L.gmlp.kind != GatedMlp::None) encode_gated_mlp(e, cmd, L, pc, second ? P.normed2.ptr() : P.normed.ptr());
         if (dump) uzu_command_buffer_encode_copy(cmd, P.resid.ptr(), P.layer_dump.ptr() + (uint64_t)i * MAX_ROWS * W * 4, (size_t)m * W * 4);
     }
     if (dump) P.dump_rows = m;
@@ -485,6 +728,11 @@ static void encode_parallel_block_readout(uzu_engine* e, uzu_command_buffer* cmd
     na.input = P.resid.ptr() + (uint64_t)row_begin * W * 4; na.scales = e->pb_final_norm.ptr(); na.output = P.normed_rows.ptr();
     na.rows = rows; na.n = W; na.groups = e->norm_groups; na.in_stride = W; na.out_stride = W; na.epsilon = e->norm_eps;
     uzu_group_rms_norm_encode(cmd, &na);
-    encode_dense(e, cmd, e->pb_head, P.normed_rows.ptr(), W, rows, P.logits_f32.ptr());
+    {
+        uzu_dense_linear_args x = dense_args(e, e->pb_head, P.normed_rows.ptr(), rows, P.logits_f32.ptr());
+        x.lda = W;
+        if (e->has_logit_scale) x.scale = e->logit_scale;
+        uzu_dense_linear_encode(cmd, &x);
+    }
     uzu_logit_cap_f32_encode(cmd, P.logits_f32.ptr(), e->logits.ptr(), rows * e->vocab, e->logit_soft_cap, e->has_logit_soft_cap);
 }

@@ -1,5 +1,6 @@
 // Glue kernels of the parallel-block family (f32 residual stream): grouped RMS norm, embedding rows into f32, the clamped gated unit,
-// tanh, residual add, logit cap, and the table router (expert-sorted pair lists + weighted combine). Everything is f32 arithmetic.
+// tanh, residual add, logit cap, and the routers (by table or by the largest logits: expert-sorted pair lists + weighted, optionally
+// gated combine). Everything is f32 arithmetic.
 #include "common.cuh"
 
 namespace uzu {
@@ -15,6 +16,8 @@ __global__ void __launch_bounds__(256) group_rms_norm_kernel(const uzu_group_rms
     const float* in = reinterpret_cast<const float*>(a.input) + (size_t)src * a.in_stride + base;
     float* out = reinterpret_cast<float*>(a.output) + (size_t)row * a.out_stride + base;
     const float* sc = a.scales ? reinterpret_cast<const float*>(a.scales) + base : nullptr;
+    float* out2 = a.output2 ? reinterpret_cast<float*>(a.output2) + (size_t)row * a.out_stride + base : nullptr;
+    const float* sc2 = a.scales2 ? reinterpret_cast<const float*>(a.scales2) + base : nullptr;
     constexpr int KEEP = 8;
     float v[KEEP];
     float ss = 0.0f;
@@ -31,9 +34,15 @@ __global__ void __launch_bounds__(256) group_rms_norm_kernel(const uzu_group_rms
 #pragma unroll
     for (int j = 0; j < KEEP; ++j) {
         const uint32_t i = threadIdx.x + j * blockDim.x;
-        if (i < part) out[i] = sc ? v[j] * inv * sc[i] : v[j] * inv;
+        if (i < part) {
+            out[i] = sc ? v[j] * inv * sc[i] : v[j] * inv;
+            if (out2) out2[i] = sc2 ? v[j] * inv * sc2[i] : v[j] * inv;
+        }
     }
-    for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < part; i += blockDim.x) out[i] = sc ? in[i] * inv * sc[i] : in[i] * inv;
+    for (uint32_t i = threadIdx.x + KEEP * blockDim.x; i < part; i += blockDim.x) {
+        out[i] = sc ? in[i] * inv * sc[i] : in[i] * inv;
+        if (out2) out2[i] = sc2 ? in[i] * inv * sc2[i] : in[i] * inv;
+    }
 }
 
 template <typename TW>
@@ -61,6 +70,16 @@ __global__ void clamped_glu_kernel(const float* gate_up, float* out, uint32_t ro
     const float g = fminf(gate_up[r * 2 * f + c], limit);
     const float u = fminf(fmaxf(gate_up[r * 2 * f + f + c], -limit), limit);
     out[idx] = g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+__global__ void silu_glu_kernel(const float* gate_up, float* out, uint32_t rows, uint32_t f) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * f) return;
+    const size_t r = idx / f, c = idx % f;
+    const float g = gate_up[r * 2 * f + c], u = gate_up[r * 2 * f + f + c];
+    out[idx] = g * (1.0f / (1.0f + expf(-g))) * u;
 }
 
 __global__ void unary_f32_kernel(const float* in, uint32_t in_stride, float* out, uint32_t out_stride, uint32_t rows, uint32_t n, uint32_t op) {
@@ -96,44 +115,26 @@ __global__ void logit_cap_f32_kernel(float* logits, __nv_bfloat16* copy, uint32_
     if (copy) copy[idx] = __float2bfloat16_rn(v);
 }
 
-// One CTA. Counting sort of the (row, slot) pairs by expert; pairs of one expert keep token order, so the lists do not depend on the
-// thread schedule. rows * top <= 1024 * top pairs; experts <= 1024.
-__global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route_args a) {
-    pdl_launch_dependents();
-    pdl_wait();
-    extern __shared__ uint32_t counts[];   // [experts + 1]
-    const uint32_t* tokens = reinterpret_cast<const uint32_t*>(a.token_ids);
-    const int32_t* table = reinterpret_cast<const int32_t*>(a.table);
-    uint32_t* offsets = reinterpret_cast<uint32_t*>(a.group_offsets);
-    uint32_t* rows_map = reinterpret_cast<uint32_t*>(a.rows_map);
-    uint32_t* pair_pos = reinterpret_cast<uint32_t*>(a.pair_pos);
-    const uint32_t pairs = a.rows * a.top;
-    uint16_t* pe = reinterpret_cast<uint16_t*>(counts + a.experts + 1);   // expert of every pair, staged once
-    for (uint32_t e = threadIdx.x; e <= a.experts; e += blockDim.x) counts[e] = 0;
+// Counting sort of the (row, slot) pairs by expert, by one CTA: `pe` (shared memory) holds the expert of every pair, `counts`
+// (shared memory, [experts + 1]) is scratch. Pairs of one expert keep token order, so the lists do not depend on the thread schedule.
+__device__ void route_sort_pairs(const uint16_t* pe, uint32_t* counts, uint32_t pairs, uint32_t top, uint32_t experts, uint32_t* offsets,
+                                 uint32_t* rows_map, uint32_t* pair_pos) {
+    for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    auto expert_of = [&](uint32_t p) -> uint32_t {
-        const uint32_t tok = tokens[p / a.top];
-        const int32_t e = tok < a.vocab ? table[(size_t)tok * a.top + p % a.top] : 0;
-        return (e >= 0 && (uint32_t)e < a.experts) ? (uint32_t)e : 0u;
-    };
-    for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const uint32_t e = expert_of(p);
-        pe[p] = (uint16_t)e;
-        atomicAdd(&counts[e + 1], 1u);
-    }
+    for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[pe[p] + 1], 1u);
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (uint32_t e = 0; e < a.experts; ++e) counts[e + 1] += counts[e];
+        for (uint32_t e = 0; e < experts; ++e) counts[e + 1] += counts[e];
     }
     __syncthreads();
-    for (uint32_t e = threadIdx.x; e <= a.experts; e += blockDim.x) offsets[e] = counts[e];
+    for (uint32_t e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = counts[e];
     // stable placement: thread e walks the pairs in order and places those of expert e
-    for (uint32_t e = threadIdx.x; e < a.experts; e += blockDim.x) {
+    for (uint32_t e = threadIdx.x; e < experts; e += blockDim.x) {
         uint32_t at = counts[e];
         if (counts[e + 1] == at) continue;
         for (uint32_t p = 0; p < pairs; ++p) {
             if (pe[p] == e) {
-                rows_map[at] = p / a.top;
+                rows_map[at] = p / top;
                 pair_pos[p] = at;
                 ++at;
             }
@@ -141,17 +142,99 @@ __global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route
     }
 }
 
-__global__ void routed_combine_kernel(const float* pairs, const uint32_t* pair_pos, float* out, uint32_t rows, uint32_t top, uint32_t n,
-                                      float weight, uint32_t accumulate) {
+// One CTA; rows * top <= 1024 * top pairs; experts <= 8192. The experts of a token come from a table row.
+__global__ void __launch_bounds__(1024) table_route_kernel(const uzu_table_route_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ uint32_t counts[];   // [experts + 1]
+    const uint32_t* tokens = reinterpret_cast<const uint32_t*>(a.token_ids);
+    const int32_t* table = reinterpret_cast<const int32_t*>(a.table);
+    const uint32_t pairs = a.rows * a.top;
+    uint16_t* pe = reinterpret_cast<uint16_t*>(counts + a.experts + 1);   // expert of every pair, staged once
+    for (uint32_t p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const uint32_t tok = tokens[p / a.top];
+        const int32_t e = tok < a.vocab ? table[(size_t)tok * a.top + p % a.top] : 0;
+        pe[p] = (uint16_t)((e >= 0 && (uint32_t)e < a.experts) ? (uint32_t)e : 0u);
+    }
+    __syncthreads();
+    route_sort_pairs(pe, counts, pairs, a.top, a.experts, reinterpret_cast<uint32_t*>(a.group_offsets), reinterpret_cast<uint32_t*>(a.rows_map),
+                     reinterpret_cast<uint32_t*>(a.pair_pos));
+}
+
+// One CTA, a warp per row: `top` rounds, each picking the best (logit, lower index first) that comes after the previous pick in that
+// order, so no list of the picked experts is kept. Weights: exp(z - z_first) over the sum of the picked ones.
+__global__ void __launch_bounds__(1024) topk_route_kernel(const uzu_topk_route_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ uint32_t counts[];   // [experts + 1]
+    const uint32_t pairs = a.rows * a.top;
+    uint16_t* pe = reinterpret_cast<uint16_t*>(counts + a.experts + 1);
+    const float* bias = reinterpret_cast<const float*>(a.bias);
+    float* weight = reinterpret_cast<float*>(a.pair_weight);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (uint32_t r = warp; r < a.rows; r += warps) {
+        const float* z = reinterpret_cast<const float*>(a.logits) + (size_t)r * a.logits_stride;
+        float prev_v = INFINITY, first = 0.0f, sum = 0.0f;
+        uint32_t prev_i = 0;
+        bool any = false;
+        for (uint32_t s = 0; s < a.top; ++s) {
+            float best_v = -INFINITY;
+            uint32_t best_i = 0xFFFFFFFFu;
+            for (uint32_t e = lane; e < a.experts; e += 32) {
+                const float v = z[e] + (bias ? bias[e] : 0.0f);
+                const bool after = !any || v < prev_v || (v == prev_v && e > prev_i);
+                if (after && (best_i == 0xFFFFFFFFu || v > best_v)) { best_v = v; best_i = e; }    // ascending e: the first of equals stays
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+                const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+                if (oi != 0xFFFFFFFFu && (best_i == 0xFFFFFFFFu || ov > best_v || (ov == best_v && oi < best_i))) { best_v = ov; best_i = oi; }
+            }
+            if (best_i == 0xFFFFFFFFu) { best_i = 0; best_v = first; }      // fewer usable logits than slots (NaNs): keep the lists well-formed
+            if (!any) first = best_v;
+            any = true;
+            prev_v = best_v; prev_i = best_i;
+            const float w = expf(best_v - first);
+            sum += w;
+            if (lane == 0) {
+                pe[r * a.top + s] = (uint16_t)best_i;
+                weight[r * a.top + s] = w;
+            }
+        }
+        __syncwarp();
+        if (lane < a.top) {
+            for (uint32_t s = lane; s < a.top; s += 32) weight[r * a.top + s] /= sum;
+        }
+    }
+    __syncthreads();
+    route_sort_pairs(pe, counts, pairs, a.top, a.experts, reinterpret_cast<uint32_t*>(a.group_offsets), reinterpret_cast<uint32_t*>(a.rows_map),
+                     reinterpret_cast<uint32_t*>(a.pair_pos));
+}
+
+__global__ void routed_combine_kernel(const uzu_routed_combine_args a) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)rows * n) return;
-    const size_t r = idx / n, c = idx % n;
+    if (idx >= (size_t)a.rows * a.n) return;
+    const size_t r = idx / a.n, c = idx % a.n;
+    const float* pairs = reinterpret_cast<const float*>(a.pairs);
+    const uint32_t* pair_pos = reinterpret_cast<const uint32_t*>(a.pair_pos);
+    const float* pw = reinterpret_cast<const float*>(a.pair_weight);
     float s = 0.0f;
-    for (uint32_t k = 0; k < top; ++k) s += pairs[(size_t)pair_pos[r * top + k] * n + c];
-    s *= weight;
-    out[idx] = accumulate ? out[idx] + s : s;
+    for (uint32_t k = 0; k < a.top; ++k) {
+        const float v = pairs[(size_t)pair_pos[r * a.top + k] * a.n + c];
+        s = pw ? fmaf(pw[r * a.top + k], v, s) : s + v;
+    }
+    s *= a.weight;
+    if (a.gate) {
+        float g = reinterpret_cast<const float*>(a.gate)[r * a.gate_ld + c];
+        if (a.gate_bias) g += reinterpret_cast<const float*>(a.gate_bias)[c];
+        s *= 1.0f / (1.0f + expf(-g));
+    }
+    if (a.col_scale) s *= reinterpret_cast<const float*>(a.col_scale)[c];
+    float* out = reinterpret_cast<float*>(a.output);
+    out[idx] = a.accumulate ? out[idx] + s : s;
 }
 
 static inline unsigned blocks256(size_t n) { return (unsigned)((n + 255) / 256); }
@@ -189,6 +272,11 @@ void uzu_clamped_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t 
     launch(cmd, "clamped_glu_kernel", clamped_glu_kernel, dim3(blocks256((size_t)rows * f)), dim3(256), 0, (const float*)gate_up, (float*)output, rows, f, limit, alpha);
 }
 
+void uzu_silu_glu_encode(uzu_command_buffer* cmd, uint64_t gate_up, uint64_t output, uint32_t rows, uint32_t f) {
+    if (!encodable(cmd, "silu_glu") || rows == 0 || f == 0) return;
+    launch(cmd, "silu_glu_kernel", silu_glu_kernel, dim3(blocks256((size_t)rows * f)), dim3(256), 0, (const float*)gate_up, (float*)output, rows, f);
+}
+
 void uzu_unary_f32_encode(uzu_command_buffer* cmd, uint64_t input, uint32_t in_stride, uint64_t output, uint32_t out_stride, uint32_t rows,
                           uint32_t n, uint32_t op) {
     if (!encodable(cmd, "unary_f32") || rows == 0 || n == 0) return;
@@ -220,11 +308,38 @@ void uzu_table_route_encode(uzu_command_buffer* cmd, const uzu_table_route_args*
     launch(cmd, "table_route_kernel", table_route_kernel, dim3(1), dim3(1024), smem, *a);
 }
 
+void uzu_topk_route_encode(uzu_command_buffer* cmd, const uzu_topk_route_args* a) {
+    if (!encodable(cmd, "topk_route")) return;
+    if (!a->logits || !a->group_offsets || !a->rows_map || !a->pair_pos || !a->pair_weight || a->top == 0 || a->experts == 0 || a->experts > 8192 ||
+        a->top > a->experts || a->logits_stride < a->experts) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "topk_route: null operand or bad expert / top count");
+        return;
+    }
+    if (a->rows == 0) return;
+    const size_t smem = (a->experts + 1) * sizeof(uint32_t) + (size_t)a->rows * a->top * sizeof(uint16_t);
+    if (smem > 48 * 1024) {
+        cmd->record_error(UZU_ERROR_UNSUPPORTED, "topk_route: rows * top too large for one pass");
+        return;
+    }
+    launch(cmd, "topk_route_kernel", topk_route_kernel, dim3(1), dim3(1024), smem, *a);
+}
+
+void uzu_routed_combine_gated_encode(uzu_command_buffer* cmd, const uzu_routed_combine_args* a) {
+    if (!encodable(cmd, "routed_combine") || a->rows == 0 || a->n == 0) return;
+    if (!a->pairs || !a->pair_pos || !a->output || a->top == 0 || (a->gate_bias && !a->gate)) {
+        cmd->record_error(UZU_ERROR_INVALID_ARGUMENT, "routed_combine: null operand, or a gate bias without a gate");
+        return;
+    }
+    uzu_routed_combine_args b = *a;
+    if (!b.gate_ld) b.gate_ld = b.n;
+    launch(cmd, "routed_combine_kernel", routed_combine_kernel, dim3(blocks256((size_t)b.rows * b.n)), dim3(256), 0, b);
+}
+
 void uzu_routed_combine_encode(uzu_command_buffer* cmd, uint64_t pairs, uint64_t pair_pos, uint64_t output, uint32_t rows, uint32_t top, uint32_t n,
                                float weight, uint32_t accumulate) {
-    if (!encodable(cmd, "routed_combine") || rows == 0 || n == 0) return;
-    launch(cmd, "routed_combine_kernel", routed_combine_kernel, dim3(blocks256((size_t)rows * n)), dim3(256), 0, (const float*)pairs, (const uint32_t*)pair_pos,
-           (float*)output, rows, top, n, weight, accumulate);
+    uzu_routed_combine_args a{};
+    a.pairs = pairs; a.pair_pos = pair_pos; a.output = output; a.rows = rows; a.top = top; a.n = n; a.weight = weight; a.accumulate = accumulate;
+    uzu_routed_combine_gated_encode(cmd, &a);
 }
 
 }  // extern "C"

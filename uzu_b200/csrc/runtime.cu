@@ -94,7 +94,8 @@ size_t uzu_abi_struct_size(const char* name) {
     UZU_SZ(uzu_delta_net_update_args) UZU_SZ(uzu_engine_options) UZU_SZ(uzu_sampling_method) UZU_SZ(uzu_model_info)
     UZU_SZ(uzu_ring_params) UZU_SZ(uzu_trie_node) UZU_SZ(uzu_kv_copy) UZU_SZ(uzu_delta_net_fused_update_args) UZU_SZ(uzu_qk_norm_config) UZU_SZ(uzu_attention_prepare_norm_args) UZU_SZ(uzu_tp_all_gather_args) UZU_SZ(uzu_activation_transform_args)
     UZU_SZ(uzu_dense_linear_args) UZU_SZ(uzu_group_rms_norm_args) UZU_SZ(uzu_table_route_args) UZU_SZ(uzu_general_delta_args) UZU_SZ(uzu_head_norm_gate_args)
-    UZU_SZ(uzu_latent_prepare_args) UZU_SZ(uzu_latent_attention_args)
+    UZU_SZ(uzu_latent_prepare_args) UZU_SZ(uzu_latent_attention_args) UZU_SZ(uzu_topk_route_args) UZU_SZ(uzu_routed_combine_args)
+    UZU_SZ(uzu_sigmoid_attention_prepare_args) UZU_SZ(uzu_sigmoid_attention_args)
 #undef UZU_SZ
     return 0;
 }
