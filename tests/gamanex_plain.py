@@ -99,10 +99,10 @@ def expert_ff(h, W, prefix):
 def moe_ff(h, W, prefix, ml):
     idx, wt = route(h, W, prefix, ml["router"]["top"])
     out = torch.zeros(h.shape[0], W[prefix + "mlp.e0.down"].shape[0], dtype=F64)
-    for t in range(h.shape[0]):
-        for s in range(idx.shape[1]):
-            e = int(idx[t, s])
-            out[t] += wt[t, s] * expert_ff(h[t:t + 1], W, f"{prefix}mlp.e{e}.")[0]
+    for e in range(ml["router"]["experts"]):
+        rows, slots = torch.nonzero(idx == e, as_tuple=True)
+        if len(rows):
+            out[rows] += wt[rows, slots][:, None] * expert_ff(h[rows], W, f"{prefix}mlp.e{e}.")
     return out
 
 

@@ -440,3 +440,93 @@ def punilix_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=0, top=2)
         layers.append(punilix_latent_layer(heads, 128, 64, 128, 512, min(1536, width), mlp_b, base=10000.0,
                                            scaling={"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}))
     return punilix_config(width, vocab, layers, norm_groups=1, eps=1e-6, logit_softcap=30.0)
+
+
+# ---------------------------------------------------------------------------------------------
+# Gamanex (parallel-block family with two norms per layer, sigmoid attention, gated sublayers): config.json {"architecture": "Gamanex",
+# "width", "vocab", "norm": {"eps"}, "logit_scale", "layers": [{"type": "attention", "mixer", "mlp"}]}; tensors embed, head, final.norm,
+# l<i>.norm1/2, l<i>.mix.*, l<i>.mlp.*, l<i>.ls1/2, l<i>.rg1/2(.b)
+# ---------------------------------------------------------------------------------------------
+def gamanex_attention_layer(heads: int, kv_heads: int, dim: int, vdim: int, mlp: dict | None, scale: float | None = None,
+                            q_temp: tuple | None = None, kv_from: int | None = None) -> dict:
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5)}
+    if q_temp is not None:
+        mixer["q_temp"] = {"coef": float(q_temp[0]), "every": int(q_temp[1])}
+    if kv_from is not None:
+        mixer["kv_from"] = int(kv_from)
+    return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+
+def gamanex_dense_mlp(ff: int) -> dict:
+    return {"kind": "dense", "ff": ff}
+
+
+def gamanex_moe_mlp(ff: int, experts: int, top: int) -> dict:
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def gamanex_config(width: int, vocab: int, layers: list, eps: float = 1e-6, logit_scale: float = 1.0) -> dict:
+    return {"architecture": "Gamanex", "width": width, "vocab": vocab, "norm": {"eps": eps}, "logit_scale": logit_scale, "layers": layers}
+
+
+def gamanex_tensors(config: dict, seed: int = 0) -> dict:
+    """Seeded random tensors of a Gamanex config: f32 values that bf16 holds exactly."""
+    rng = np.random.default_rng(seed)
+    W, V = config["width"], config["vocab"]
+
+    def bf(x):
+        return st_bits_to_f32(f32_to_bf16_bits(np.asarray(x, np.float32)))
+
+    def mat(rows, cols, gain=1.0):
+        return bf(rng.standard_normal((rows, cols), dtype=np.float32) * (gain / np.sqrt(cols)))
+
+    def vec(n, mean=1.0, spread=0.1):
+        return bf(mean + spread * rng.standard_normal(n, dtype=np.float32))
+
+    t = {"embed": mat(V, W, np.sqrt(W)), "head": mat(V, W, 2.0), "final.norm": vec(W)}
+    for i, L in enumerate(config["layers"]):
+        p = f"l{i}."
+        m = L["mixer"]
+        H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        t[p + "norm1"] = vec(W)
+        t[p + "mix.q"], t[p + "mix.q.norm"] = mat(H * D, W), vec(H * D, 1.0, 0.2)
+        if m.get("kv_from") is None:
+            t[p + "mix.k"], t[p + "mix.v"], t[p + "mix.k.norm"] = mat(G * D, W), mat(G * Dv, W), vec(G * D, 1.0, 0.2)
+        t[p + "mix.r1"] = bf(np.abs(vec(H, 0.5, 0.3)) + 0.05)
+        t[p + "mix.r2"] = bf(np.abs(vec(H, 0.3, 0.2)) + 0.05)
+        t[p + "mix.pb"] = vec(H, -1.0, 0.5)
+        t[p + "mix.o"] = mat(W, H * Dv)
+        t[p + "ls1"], t[p + "rg1"], t[p + "rg1.b"] = vec(W, 0.7, 0.2), mat(W, W), vec(W, 0.3, 0.5)
+        ml = L.get("mlp")
+        if ml is None:
+            continue
+        t[p + "norm2"] = vec(W)
+        t[p + "ls2"], t[p + "rg2"], t[p + "rg2.b"] = vec(W, 0.7, 0.2), mat(W, W), vec(W, 0.3, 0.5)
+        if ml["kind"] == "dense":
+            t[p + "mlp.up"], t[p + "mlp.down"] = mat(ml["ff"], W, 1.5), mat(W, ml["ff"])
+        else:
+            f, E = ml["expert"]["ff"], ml["router"]["experts"]
+            t[p + "mlp.router"], t[p + "mlp.router.b"] = mat(E, W, 2.0), vec(E, 0.0, 0.5)
+            for x in range(E):
+                q = f"{p}mlp.e{x}."
+                t[q + "gate"], t[q + "up"], t[q + "down"] = mat(f, W, 1.5), mat(f, W, 1.5), mat(W, f)
+    return t
+
+
+def write_gamanex_model(config: dict, path, seed: int = 0, tensors: dict | None = None) -> Path:
+    """config.json + model.safetensors (bf16). `tensors` overrides the seeded random ones (values are rounded to bf16)."""
+    return write_punilix_model(config, path, seed, tensors if tensors is not None else gamanex_tensors(config, seed))
+
+
+def gamanex_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=0, top=2, kv_heads=None) -> dict:
+    """A layer stack of realistic sizes for benchmarks: per block one attention layer that keeps its keys and values and one that
+    borrows them; the feed-forward is dense, or (second layer of a block) routed experts of the same active size when `experts` > 0."""
+    ff = ff or 4 * width
+    heads = max(width // 128, 1)
+    kv = kv_heads or heads
+    layers = []
+    for b in range(blocks):
+        mlp_b = gamanex_moe_mlp(ff // top, experts, top) if experts else gamanex_dense_mlp(ff)
+        layers.append(gamanex_attention_layer(heads, kv, 128, 128, gamanex_dense_mlp(ff), q_temp=(0.3, 256)))
+        layers.append(gamanex_attention_layer(heads, kv, 128, 128, mlp_b, q_temp=(0.3, 256), kv_from=2 * b))
+    return gamanex_config(width, vocab, layers, eps=1e-6, logit_scale=0.25)
