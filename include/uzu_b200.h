@@ -563,7 +563,7 @@ UZU_API void uzu_sigmoid_attention_prepare_encode(uzu_command_buffer* cmd, const
  * kv_heads*vdim]; query head h reads key / value head h / (heads / kv_heads):
  *   s(t, h, j) = scale * query[t, h, :] . keys[j, g, :] - dist_r1[h] * ln(1 + dist_r2[h] * (p - j)) + head_bias[h],   j <= p
  *   out[t, h, :] = sum_j sigmoid(s) * values[j, g, :]        (f32 [rows, heads*vdim]; weights are not normalised over j)
- * Scores, weights and sums are f32. bf16 caches with rows >= 16 and dim, vdim multiples of 16 up to 128 run on the tensor pipe: query
+ * Scores, weights and sums are f32. bf16 caches with rows >= 64 and dim, vdim multiples of 16 up to 128 run on the tensor pipe: query
  * and weight each as a sum of two bf16 numbers (hi + lo), so their rounding stays below 2^-16. */
 typedef struct uzu_sigmoid_attention_args {
     uint64_t query, keys, values, out, dynamic_position;

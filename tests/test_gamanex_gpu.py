@@ -189,7 +189,8 @@ def new_cache(ctx, positions, kv_heads, dim, vdim, f32_cache):
 
 @pytest.mark.parametrize("T,prefix,heads,kv_heads,dim,vdim,temp", [
     (1, 0, 2, 2, 8, 8, None), (1, 77, 6, 2, 16, 24, (0.4, 7)), (40, 0, 4, 1, 32, 16, (0.25, 16)), (70, 130, 3, 3, 9, 7, (1.5, 1)),
-    (200, 65, 8, 4, 64, 64, (0.3, 256)), (130, 2, 2, 1, 128, 96, None), (17, 300, 1, 1, 260, 40, (0.1, 50))])
+    (200, 65, 8, 4, 64, 64, (0.3, 256)), (130, 2, 2, 1, 128, 96, None), (17, 300, 1, 1, 260, 40, (0.1, 50)),
+    (64, 0, 2, 2, 16, 16, None), (100, 40, 4, 2, 32, 48, (0.2, 30)), (260, 1000, 2, 1, 96, 96, (0.3, 256)), (129, 63, 3, 1, 80, 112, None)])
 @pytest.mark.parametrize("f32_cache", [True, False])
 def test_sigmoid_attention_kernels(ctx, T, prefix, heads, kv_heads, dim, vdim, temp, f32_cache):
     """A prefix pass, then the pass under test on top of it (prompt portion or one decoded token), with and without key splits."""
@@ -216,7 +217,7 @@ def test_one_far_key_among_hundreds_and_the_causal_edge(ctx, far, f32_cache):
     """Every key but one scores far below zero; the one at position `far` scores high. Queries before it must not see it (also not the query one
     place before), queries from it on get its value times a weight that falls with the distance. Prompt rows and one decoded row."""
     rng = np.random.default_rng(far)
-    heads, dim, vdim, n, T = 2, 16, 8, 640, 130
+    heads, dim, vdim, n, T = 2, 16, 16, 640, 130
     k = rng.standard_normal((n, dim), dtype=np.float32) * 0.05
     k[:, 3] = 0
     k[far] = 0

@@ -8,7 +8,7 @@
 //            four keys of a warp in flight; because the weights are not normalised the partial results of the splits simply add: the
 //            last split to finish (a ticket per query and head) adds them in split order, so no second launch and no dependence on
 //            the order of arrival;
-//   attend, tensor pipe (sigmoid_attention_mma_kernel): bf16 caches and passes of >= 16 rows.
+//   attend, tensor pipe (sigmoid_attention_mma_kernel): bf16 caches and passes of >= 64 rows (described at the kernel).
 // The cache holds bf16 or f32 rows; scores, weights and sums are f32.
 #include "common.cuh"
 
@@ -253,7 +253,208 @@ void uzu_sigmoid_attention_encode(uzu_command_buffer* cmd, const uzu_sigmoid_att
 
 }  // extern "C"
 
+// ---- tensor pipe (bf16 caches, passes of >= 64 rows) ----------------------------------------------------------------------------------
+// One CTA = 64 query rows of one head (4 warps x 16 rows), key tiles of 64 from position 0 up to the CTA's last row; the next tile's
+// keys and values arrive by cp.async while the current one is used. mma.sync.m16n8k16 (bf16 x bf16 -> f32):
+//   S = (q * scale) . K^T     with q = q_hi + q_lo, two bf16 numbers per f32 query entry (two MMAs per tile of S);
+//   w = sigmoid(S - r1 ln(1 + r2 (i - j)) + pb), 0 for j > i, in f32 on the accumulator fragment;
+//   O += w . V                with w = w_hi + w_lo again, the accumulator fragment of S re-used as the A fragment (two adjacent
+//                             8-key tiles form one 16-key step), V fragments by ldmatrix.trans from the row-major tile.
+// The split keeps the error of the query and of the weights below 2^-16 relative, so only the cache's own bf16 rounding remains.
 namespace uzu {
-// the tensor-pipe form is added below this line
-bool encode_sigmoid_attention_mma(uzu_command_buffer*, const uzu_sigmoid_attention_args&) { return false; }
+
+namespace {
+
+constexpr int SM_BM = 64, SM_BN = 64, SM_PAD = 8;
+
+__device__ __forceinline__ void sm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void sm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+__device__ __forceinline__ void sm_cp_async16(void* smem_ptr, const void* gmem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(addr), "l"(gmem_ptr) : "memory");
+}
+
+// x = hi + lo with both parts bf16; a pair of values packed for an MMA fragment
+__device__ __forceinline__ void sm_split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+    const __nv_bfloat162 h = __halves2bfloat162(h0, h1);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+}  // namespace
+
+// DK = most 16-channel steps of a key row (dim / 16 rounded up to 4 or 8), DV = most 16-column blocks of a value row
+template <int DK, int DV>
+__global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const uzu_sigmoid_attention_args a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    const uint32_t dim = a.dim, vdim = a.vdim, ldk = dim + SM_PAD, ldv = vdim + SM_PAD, dk = dim / 16, dv = vdim / 16;
+    __nv_bfloat16* q_hi = reinterpret_cast<__nv_bfloat16*>(sm_raw);      // [64][ldk]
+    __nv_bfloat16* q_lo = q_hi + SM_BM * ldk;
+    __nv_bfloat16* k_s = q_lo + SM_BM * ldk;                             // [2][64][ldk]
+    __nv_bfloat16* v_s = k_s + 2 * SM_BN * ldk;                          // [2][64][ldv]
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    const uint32_t m0 = (gridDim.x - 1 - blockIdx.x) * SM_BM, h = blockIdx.y;      // the rows with the most keys start first
+    const uint32_t kvh = h / (a.heads / a.kv_heads);
+    const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
+    const uint32_t rows_here = min((uint32_t)SM_BM, a.rows - m0);
+    const uint32_t nkeys = prefix + m0 + rows_here, ntiles = (nkeys + SM_BN - 1) / SM_BN;
+    const float r1 = a.dist_r1 ? reinterpret_cast<const float*>(a.dist_r1)[h] : 0.0f;
+    const float r2 = a.dist_r2 ? reinterpret_cast<const float*>(a.dist_r2)[h] : 0.0f;
+    const float pb = a.head_bias ? reinterpret_cast<const float*>(a.head_bias)[h] : 0.0f;
+    {   // the query tile, scaled, as hi + lo
+        const float* q = reinterpret_cast<const float*>(a.query) + (size_t)m0 * a.heads * dim + (size_t)h * dim;
+        const uint32_t pairs = dim / 2;
+        for (uint32_t i = tid; i < SM_BM * pairs; i += blockDim.x) {
+            const uint32_t r = i / pairs, c = (i - r * pairs) * 2;
+            float2 x = make_float2(0.0f, 0.0f);
+            if (r < rows_here) x = *reinterpret_cast<const float2*>(q + (size_t)r * a.heads * dim + c);
+            uint32_t hi, lo;
+            sm_split_pair(x.x * a.scale, x.y * a.scale, hi, lo);
+            *reinterpret_cast<uint32_t*>(q_hi + r * ldk + c) = hi;
+            *reinterpret_cast<uint32_t*>(q_lo + r * ldk + c) = lo;
+        }
+    }
+    const __nv_bfloat16* keys = reinterpret_cast<const __nv_bfloat16*>(a.keys) + (size_t)kvh * dim;
+    const __nv_bfloat16* values = reinterpret_cast<const __nv_bfloat16*>(a.values) + (size_t)kvh * vdim;
+    const size_t kstride = (size_t)a.kv_heads * dim, vstride = (size_t)a.kv_heads * vdim;
+    auto load_tile = [&](uint32_t t, uint32_t buf) {      // rows past the last key are zero: cache pages beyond the context may not exist
+        const uint32_t j0 = t * SM_BN, kc = dim / 8, vc = vdim / 8;
+        for (uint32_t i = tid; i < SM_BN * kc; i += blockDim.x) {
+            const uint32_t r = i / kc, c = (i - r * kc) * 8;
+            __nv_bfloat16* dst = k_s + (buf * SM_BN + r) * ldk + c;
+            if (j0 + r < nkeys) sm_cp_async16(dst, keys + (size_t)(j0 + r) * kstride + c);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        for (uint32_t i = tid; i < SM_BN * vc; i += blockDim.x) {
+            const uint32_t r = i / vc, c = (i - r * vc) * 8;
+            __nv_bfloat16* dst = v_s + (buf * SM_BN + r) * ldv + c;
+            if (j0 + r < nkeys) sm_cp_async16(dst, values + (size_t)(j0 + r) * vstride + c);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float o[2 * DV][4];
+#pragma unroll
+    for (int n = 0; n < 2 * DV; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[n][c] = 0.0f;
+    const uint32_t row_lo = warp * 16 + g;                     // this thread's rows of the tile: row_lo and row_lo + 8
+    const uint32_t i_lo = prefix + m0 + row_lo, i_warp_last = prefix + m0 + warp * 16 + 15;
+    load_tile(0, 0);
+    for (uint32_t t = 0; t < ntiles; ++t) {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();                                       // tile t is in place, tile t - 1 is used up
+        if (t + 1 < ntiles) load_tile(t + 1, (t + 1) & 1);
+        const uint32_t j0 = t * SM_BN;
+        if (j0 > i_warp_last) continue;                        // nothing of this tile is visible to the warp's rows
+        const __nv_bfloat16* kt = k_s + (t & 1) * SM_BN * ldk;
+        const __nv_bfloat16* vt = v_s + (t & 1) * SM_BN * ldv;
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[n][c] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < DK; ++kk) {
+            if ((uint32_t)kk < dk) {
+                uint32_t ah[4], al[4];
+                const uint32_t off = row_lo * ldk + kk * 16 + t4 * 2;
+                ah[0] = *reinterpret_cast<const uint32_t*>(q_hi + off);
+                ah[1] = *reinterpret_cast<const uint32_t*>(q_hi + off + 8 * ldk);
+                ah[2] = *reinterpret_cast<const uint32_t*>(q_hi + off + 8);
+                ah[3] = *reinterpret_cast<const uint32_t*>(q_hi + off + 8 * ldk + 8);
+                al[0] = *reinterpret_cast<const uint32_t*>(q_lo + off);
+                al[1] = *reinterpret_cast<const uint32_t*>(q_lo + off + 8 * ldk);
+                al[2] = *reinterpret_cast<const uint32_t*>(q_lo + off + 8);
+                al[3] = *reinterpret_cast<const uint32_t*>(q_lo + off + 8 * ldk + 8);
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    const __nv_bfloat16* kb = kt + (n * 8 + g) * ldk + kk * 16 + t4 * 2;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb), b1 = *reinterpret_cast<const uint32_t*>(kb + 8);
+                    sm_mma(s[n], ah, b0, b1);
+                    sm_mma(s[n], al, b0, b1);
+                }
+            }
+        }
+        // weights on the fragment: element c of tile n is row row_lo + 8 * (c >> 1), key j0 + n * 8 + t4 * 2 + (c & 1)
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t i = i_lo + 8 * (c >> 1), j = j0 + n * 8 + t4 * 2 + (c & 1);
+                float w = 0.0f;
+                if (j <= i) {
+                    const float score = s[n][c] - r1 * __logf(fmaf(r2, (float)(i - j), 1.0f)) + pb;
+                    w = __fdividef(1.0f, 1.0f + __expf(-score));
+                }
+                s[n][c] = w;
+            }
+#pragma unroll
+        for (int kk = 0; kk < SM_BN / 16; ++kk) {
+            uint32_t ph[4], pl[4];
+            sm_split_pair(s[2 * kk][0], s[2 * kk][1], ph[0], pl[0]);
+            sm_split_pair(s[2 * kk][2], s[2 * kk][3], ph[1], pl[1]);
+            sm_split_pair(s[2 * kk + 1][0], s[2 * kk + 1][1], ph[2], pl[2]);
+            sm_split_pair(s[2 * kk + 1][2], s[2 * kk + 1][3], ph[3], pl[3]);
+#pragma unroll
+            for (int n = 0; n < DV; ++n) {
+                if ((uint32_t)n < dv) {
+                    uint32_t b[4];
+                    sm_ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + n * 16 + (lane >> 4) * 8);
+                    sm_mma(o[2 * n], ph, b[0], b[1]);
+                    sm_mma(o[2 * n], pl, b[0], b[1]);
+                    sm_mma(o[2 * n + 1], ph, b[2], b[3]);
+                    sm_mma(o[2 * n + 1], pl, b[2], b[3]);
+                }
+            }
+        }
+    }
+    float* out = reinterpret_cast<float*>(a.out) + (size_t)m0 * a.heads * vdim + (size_t)h * vdim;
+#pragma unroll
+    for (int n = 0; n < 2 * DV; ++n) {
+        if ((uint32_t)n < 2 * dv) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t r = row_lo + 8 * half;
+                if (r < rows_here) *reinterpret_cast<float2*>(out + (size_t)r * a.heads * vdim + n * 8 + t4 * 2) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+            }
+        }
+    }
+}
+
+template <int DK, int DV>
+static void launch_sigmoid_attention_mma(uzu_command_buffer* cmd, const uzu_sigmoid_attention_args& a) {
+    const size_t smem = ((size_t)4 * SM_BM * (a.dim + SM_PAD) + (size_t)2 * SM_BN * (a.vdim + SM_PAD)) * sizeof(__nv_bfloat16);
+    static std::atomic<uint64_t> opt_in{0};
+    opt_in_dynamic_smem(cmd, sigmoid_attention_mma_kernel<DK, DV>, (int)smem, opt_in);
+    launch(cmd, "sigmoid_attention_mma_kernel", sigmoid_attention_mma_kernel<DK, DV>, dim3((a.rows + SM_BM - 1) / SM_BM, a.heads), dim3(128), smem, a);
+}
+
+// Shapes the tensor-pipe kernel takes: bf16 caches, passes of >= 64 rows, key and value sizes multiples of 16 up to 128, 16-byte aligned
+// caches and an 8-byte aligned query / output. Everything else (and every f32 cache) runs the plain kernel.
+bool encode_sigmoid_attention_mma(uzu_command_buffer* cmd, const uzu_sigmoid_attention_args& a) {
+    static const bool off = getenv("UZU_SIGMOID_NO_MMA") != nullptr;       // A/B runs
+    if (off || a.cache_dt != UZU_DT_BF16 || a.rows < SM_BM || a.dim % 16 || a.vdim % 16 || a.dim > 128 || a.vdim > 128) return false;
+    if ((a.keys & 15) || (a.values & 15) || (a.query & 7) || (a.out & 7)) return false;
+    const bool k8 = a.dim > 64, v8 = a.vdim > 64;
+    if (k8 && v8) launch_sigmoid_attention_mma<8, 8>(cmd, a);
+    else if (k8) launch_sigmoid_attention_mma<8, 4>(cmd, a);
+    else if (v8) launch_sigmoid_attention_mma<4, 8>(cmd, a);
+    else launch_sigmoid_attention_mma<4, 4>(cmd, a);
+    return true;
+}
+
 }  // namespace uzu
