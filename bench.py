@@ -703,7 +703,7 @@ def run_batched(args, eng, ctx, dist, rank, world, local_rank, workload, prefill
         dist.destroy_process_group()
 
 
-# ---- model-family comparison (--family): Punilix beside the closest existing family at equal layer sizes ------------------------------
+# ---- model-family comparison (--family): a dense-weight family beside the closest existing family at equal layer sizes ----------------
 FAMILY_SIZES = {
     # name: (width, feed-forward, blocks of [recurrent layer, attention layer], vocab)
     "1k": (1024, 4096, 3, 32768),
@@ -712,9 +712,10 @@ FAMILY_SIZES = {
 }
 
 
-def family_models(size: str):
-    """(Punilix checkpoint, closest existing model's checkpoint) at one size: alternating recurrent / attention layers of the same
-    width, feed-forward size, head count and layer count; random weights."""
+def family_models(size: str, family: str = "punilix"):
+    """[(name, checkpoint, stored bytes per weight)]: the family's model and the closest existing model's at one size: two layers per
+    block of the same width, feed-forward size, head count and layer count; random weights. Punilix stands beside the 4-bit hybrid
+    (gated attention + DeltaNet); Gamanex (attention layers that keep or borrow their cache, dense feed-forwards) beside Punilix."""
     from uzu_b200 import synth
     width, ff, blocks, vocab = FAMILY_SIZES[size]
     base = Path(os.environ.get("UZU_MODEL_CACHE", "/dev/shm/uzu_b200_models"))
@@ -723,6 +724,12 @@ def family_models(size: str):
     if not (pdir / ".done").exists():
         synth.write_punilix_model(synth.punilix_preset(width=width, vocab=vocab, blocks=blocks, ff=ff), pdir, seed=0)
         (pdir / ".done").write_text("ok")
+    if family == "gamanex":
+        gdir = base / f"gamanex-{size}"
+        if not (gdir / ".done").exists():
+            synth.write_gamanex_model(synth.gamanex_preset(width=width, vocab=vocab, blocks=blocks, ff=ff), gdir, seed=0)
+            (gdir / ".done").write_text("ok")
+        return [("gamanex", gdir, 2.0), ("closest_existing", pdir, 2.0)]
     heads = max(width // 128, 1)
     spec = synth.ModelSpec(name=f"hybrid-{size}", model_dim=width, hidden_dim=ff, vocab_size=vocab,
                            layer_kinds=["delta", "attn"] * blocks, num_heads=heads, num_groups=max(heads // 4, 1), head_dim=128,
@@ -734,12 +741,12 @@ def family_models(size: str):
     if not (qdir / ".done").exists():
         synth.write_model(spec, qdir, seed=0)
         (qdir / ".done").write_text("ok")
-    return pdir, qdir
+    return [("punilix", pdir, 2.0), ("closest_existing", qdir, 0.5625)]      # bf16, or 4-bit codes + a bf16 scale and a 4-bit zero point per 64
 
 
 def family_compare(args):
-    """One JSON line per size: prefill and decode throughput of Punilix and of the closest existing family (gated attention + DeltaNet,
-    4-bit weights) with the same layer sizes. Prefill: a prompt of --prefill tokens (default 1024) through prefill(), wall clock around
+    """One JSON line per size: prefill and decode throughput of the family and of the closest existing family (family_models) with the
+    same layer sizes. Prefill: a prompt of --prefill tokens (default 1024) through prefill(), wall clock around
     the synchronous call, best of 3. Decode: decode_timed (CUDA events around device-chained steps), after warm-up. Fractions are of the
     measured peaks: decode against the bytes a token must read (weights + cache rows + states), prefill against 2 * tokens * weights."""
     from uzu_b200 import binding as B
@@ -751,10 +758,10 @@ def family_compare(args):
     sizes = [x for x in (args.family_sizes.split(",") if args.family_sizes else ["1k", "2k"]) if x]
     with B.Context(0) as ctx:
         for size in sizes:
-            pdir, qdir = family_models(size)
-            line = {"family_compare": size, "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
+            models = family_models(size, args.family)
+            line = {"family_compare": size, "family": args.family, "closest_existing": "punilix (bf16)" if args.family == "gamanex" else "gated attention + DeltaNet hybrid (int4)", "prefill_tokens": prompt_len, "decode_steps": steps, "peaks": {"hbm_gbs": hbm, "hbm_source": hbm_src,
                                                                                                          "tensor_tflops": tens, "tensor_source": tens_src}}
-            for name, d in (("punilix", pdir), ("closest_existing", qdir)):
+            for name, d, bytes_per_weight in models:
                 with B.Engine(ctx, d, max_context_length=prompt_len + steps + 64, use_cuda_graph=not args.no_graph) as eng:
                     vocab = eng.info.vocab_size
                     prompt = ((np.arange(prompt_len, dtype=np.int64) * 7919 + 13) % vocab).astype(np.uint32)
@@ -771,7 +778,7 @@ def family_compare(args):
                     sec = eng.decode_timed(steps)
                     launches = (eng.launch_count - l0) / steps
                     info = eng.info
-                    params = info.weight_bytes_per_token / (2.0 if name == "punilix" else 0.5625)      # bf16, or 4-bit codes + a bf16 scale and a 4-bit zero point per 64
+                    params = info.weight_bytes_per_token / bytes_per_weight
                     step_bytes = info.weight_bytes_per_token + info.kv_bytes_per_token_per_ctx * (prompt_len + steps / 2) + info.state_bytes_per_token
                     line[name] = {
                         "prefill_tok_s": prompt_len / best, "prefill_ms": 1e3 * best,
@@ -800,7 +807,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=1, help="decode this many independent sequences together (<= 16), one weight pass per step")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size: shard ONE model over this many ranks (= --gpus) instead of replicas")
-    ap.add_argument("--family", choices=["punilix"], default=None,
+    ap.add_argument("--family", choices=["punilix", "gamanex"], default=None,
                     help="instead of the headline workload: prefill / decode throughput of this model family beside the closest existing one at equal layer sizes (1 GPU)")
     ap.add_argument("--family-sizes", default="", help="comma list of " + ", ".join(sorted(FAMILY_SIZES)) + " (default 1k,2k)")
     args = ap.parse_args()
