@@ -281,12 +281,19 @@ static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string
     uint32_t n_cache = 0;
     const auto& lcs = cfg.at("layers").arr;
     e->layers.resize(lcs.size());
-    auto sublayer_gate = [&](SublayerGate& g, std::vector<float>& stacked, uint32_t rows_before, const std::string& p, const char* scale, const char* gate) {
-        g.present = true;
+    // the gate matrix joins the sublayer's stacked projection (returns the rows it added); a checkpoint without the gate or without the
+    // scale of a sublayer leaves that factor out
+    auto sublayer_gate = [&](SublayerGate& g, std::vector<float>& stacked, uint32_t rows_before, const std::string& p, const char* scale, const char* gate) -> uint32_t {
+        uint32_t added = 0;
         g.offset = rows_before;
-        append(stacked, read_floats(pl, p + gate, {W, W}));
-        g.bias = upload_f32(e, read_floats(pl, p + gate + ".b", {W}).v);
-        g.scale = upload_f32(e, read_floats(pl, p + scale, {W}).v);
+        if (pl.tensors.count(p + gate)) {
+            append(stacked, read_floats(pl, p + gate, {W, W}));
+            g.bias = upload_f32(e, read_floats(pl, p + gate + ".b", {W}).v);
+            added = W;
+        }
+        if (pl.tensors.count(p + scale)) g.scale = upload_f32(e, read_floats(pl, p + scale, {W}).v);
+        g.present = g.bias.b || g.scale.b;
+        return added;
     };
     for (size_t i = 0; i < lcs.size(); ++i) {
         const Json& lc = lcs[i];
@@ -338,8 +345,8 @@ static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string
             kvb += (uint64_t)(kn + vn) * storage_size(e->store_dt);
             n_cache++;
         }
-        sublayer_gate(L.mix_gate, in, rows, p, "ls1", "rg1");
-        A.in = upload_matrix(e, in, rows + W, W);
+        rows += sublayer_gate(L.mix_gate, in, rows, p, "ls1", "rg1");
+        A.in = upload_matrix(e, in, rows, W);
         A.out = upload_matrix(e, read_floats(pl, p + "mix.o", {W, A.heads * A.vdim}).v, W, A.heads * A.vdim);
         A.dist_r1 = upload_f32(e, read_floats(pl, p + "mix.r1", {A.heads}).v);
         A.dist_r2 = upload_f32(e, read_floats(pl, p + "mix.r2", {A.heads}).v);
@@ -360,8 +367,8 @@ static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string
             if (M.f == 0) throw std::runtime_error(p + "mlp: ff must be positive");
             std::vector<float> up;
             append(up, read_floats(pl, p + "mlp.up", {M.f, W}));
-            sublayer_gate(L.mlp_gate, up, M.f, p, "ls2", "rg2");
-            M.gate_up = upload_matrix(e, up, M.f + W, W);
+            const uint32_t gate_rows = sublayer_gate(L.mlp_gate, up, M.f, p, "ls2", "rg2");
+            M.gate_up = upload_matrix(e, up, M.f + gate_rows, W);
             M.down = upload_matrix(e, read_floats(pl, p + "mlp.down", {W, M.f}).v, W, M.f);
             wbytes += M.gate_up.bytes + M.down.bytes;
         } else if (kind == "moe") {
@@ -374,8 +381,8 @@ static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string
                 throw std::runtime_error(p + "mlp: bad expert / top counts");
             std::vector<float> ro, gu, dn;
             append(ro, read_floats(pl, p + "mlp.router", {M.experts, W}));
-            sublayer_gate(L.mlp_gate, ro, M.experts, p, "ls2", "rg2");
-            M.router = upload_matrix(e, ro, M.experts + W, W);
+            const uint32_t gate_rows = sublayer_gate(L.mlp_gate, ro, M.experts, p, "ls2", "rg2");
+            M.router = upload_matrix(e, ro, M.experts + gate_rows, W);
             M.router_bias = upload_f32(e, read_floats(pl, p + "mlp.router.b", {M.experts}).v);
             for (uint32_t x = 0; x < M.experts; ++x) {
                 const std::string q = p + "mlp.e" + std::to_string(x) + ".";
@@ -501,8 +508,8 @@ static void encode_into_residual(uzu_engine* e, uzu_command_buffer* cmd, const D
     uzu_dense_linear_args x = dense_args(e, w, a, rows, e->pb.resid.ptr());
     x.lda = lda; x.accumulate = 1; x.a_op = a_op;
     if (g && g->present) {
-        x.gate = gate_block + (uint64_t)g->offset * 4; x.gate_ld = gate_ld;
-        x.gate_bias = g->bias.ptr(); x.col_scale = g->scale.ptr();
+        if (g->bias.b) { x.gate = gate_block + (uint64_t)g->offset * 4; x.gate_ld = gate_ld; x.gate_bias = g->bias.ptr(); }
+        if (g->scale.b) x.col_scale = g->scale.ptr();
     }
     uzu_dense_linear_encode(cmd, &x);
 }
@@ -686,8 +693,8 @@ static void encode_gated_mlp(uzu_engine* e, uzu_command_buffer* cmd, const Layer
     if (M.kind == GatedMlp::RoutedExperts) { ca.pair_weight = P.pair_weight.ptr(); ca.weight = 1.0f; }
     else ca.weight = 1.0f / (float)M.top;
     if (L.mlp_gate.present) {
-        ca.gate = P.proj2.ptr() + (uint64_t)L.mlp_gate.offset * 4; ca.gate_ld = M.router.rows;
-        ca.gate_bias = L.mlp_gate.bias.ptr(); ca.col_scale = L.mlp_gate.scale.ptr();
+        if (L.mlp_gate.bias.b) { ca.gate = P.proj2.ptr() + (uint64_t)L.mlp_gate.offset * 4; ca.gate_ld = M.router.rows; ca.gate_bias = L.mlp_gate.bias.ptr(); }
+        if (L.mlp_gate.scale.b) ca.col_scale = L.mlp_gate.scale.ptr();
     }
     uzu_routed_combine_gated_encode(cmd, &ca);
 }
