@@ -82,7 +82,7 @@ def test_dense_feed_forward_squares_the_positive_part():
 
 def test_synthetic_checkpoint_layout(tmp_path):
     cfg = synth.gamanex_config(32, 40, [
-        synth.gamanex_attention_layer(4, 2, 8, 6, synth.gamanex_dense_mlp(20), q_temp=(0.3, 16)),
+        synth.gamanex_attention_layer(4, 2, 8, 6, synth.gamanex_dense_mlp(20), q_temp=(0.45, 16)),
         synth.gamanex_attention_layer(4, 2, 8, 6, synth.gamanex_moe_mlp(10, 3, 2), kv_from=0),
         synth.gamanex_attention_layer(2, 2, 4, 4, None),
     ], logit_scale=0.5)

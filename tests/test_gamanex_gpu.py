@@ -99,7 +99,7 @@ def test_silu_gated_unit(ctx, m):
         close(bd.numpy(np.float32, (m, f)), (g * torch.sigmoid(g) * u).numpy(), 5e-6, "paired silu unit")
 
 
-@pytest.mark.parametrize("rows,experts,top,stride", [(1, 12, 4, 12), (9, 5, 5, 9), (70, 40, 1, 64), (1024, 7, 3, 7), (6, 130, 8, 130)])
+@pytest.mark.parametrize("rows,experts,top,stride", [(1, 10, 4, 10), (9, 5, 5, 9), (70, 40, 1, 64), (1024, 7, 3, 7), (6, 130, 8, 130)])
 def test_router_picks_the_largest_and_sorts_pairs_by_expert(ctx, rows, experts, top, stride):
     rng = np.random.default_rng(rows + experts)
     z = rng.standard_normal((rows, stride), dtype=np.float32)
@@ -189,8 +189,8 @@ def new_cache(ctx, positions, kv_heads, dim, vdim, f32_cache):
 
 @pytest.mark.parametrize("T,prefix,heads,kv_heads,dim,vdim,temp", [
     (1, 0, 2, 2, 8, 8, None), (1, 77, 6, 2, 16, 24, (0.4, 7)), (40, 0, 4, 1, 32, 16, (0.25, 16)), (70, 130, 3, 3, 9, 7, (1.5, 1)),
-    (200, 65, 8, 4, 64, 64, (0.3, 256)), (130, 2, 2, 1, 128, 96, None), (17, 300, 1, 1, 260, 40, (0.1, 50)),
-    (64, 0, 2, 2, 16, 16, None), (100, 40, 4, 2, 32, 48, (0.2, 30)), (260, 1000, 2, 1, 96, 96, (0.3, 256)), (129, 63, 3, 1, 80, 112, None)])
+    (200, 65, 8, 4, 64, 64, (0.35, 128)), (130, 2, 2, 1, 128, 96, None), (17, 300, 1, 1, 260, 40, (0.1, 50)),
+    (64, 0, 2, 2, 16, 16, None), (100, 40, 4, 2, 32, 48, (0.2, 30)), (260, 1000, 2, 1, 96, 80, (0.15, 512)), (129, 63, 3, 1, 80, 112, None)])
 @pytest.mark.parametrize("f32_cache", [True, False])
 def test_sigmoid_attention_kernels(ctx, T, prefix, heads, kv_heads, dim, vdim, temp, f32_cache):
     """A prefix pass, then the pass under test on top of it (prompt portion or one decoded token), with and without key splits."""
@@ -280,8 +280,8 @@ def config_b():
 def config_c():
     """Sizes that fit no vector width: width 90, odd head sizes 9 / 7 (bf16 rows that start at odd elements), odd feed-forwards, 3 experts."""
     return P.make_config(90, 77, [
-        P.attention_layer(4, 2, 9, 7, scale=0.4, q_temp=(0.3, 3), mlp=P.moe_mlp(11, 3, 2)),
-        P.attention_layer(2, 1, 18, 20, q_temp=(0.3, 64), mlp=P.dense_mlp(51)),
+        P.attention_layer(4, 2, 9, 7, scale=0.4, q_temp=(0.35, 3), mlp=P.moe_mlp(11, 3, 2)),
+        P.attention_layer(2, 1, 18, 20, q_temp=(0.15, 64), mlp=P.dense_mlp(51)),
         P.attention_layer(4, 2, 9, 7, scale=0.2, kv_from=0, mlp=None),
     ], eps=1e-5, logit_scale=0.3)
 

@@ -527,6 +527,6 @@ def gamanex_preset(width=2048, vocab=32768, blocks=6, ff=None, experts=0, top=2,
     layers = []
     for b in range(blocks):
         mlp_b = gamanex_moe_mlp(ff // top, experts, top) if experts else gamanex_dense_mlp(ff)
-        layers.append(gamanex_attention_layer(heads, kv, 128, 128, gamanex_dense_mlp(ff), q_temp=(0.3, 256)))
-        layers.append(gamanex_attention_layer(heads, kv, 128, 128, mlp_b, q_temp=(0.3, 256), kv_from=2 * b))
-    return gamanex_config(width, vocab, layers, eps=1e-6, logit_scale=0.25)
+        layers.append(gamanex_attention_layer(heads, kv, 128, 128, gamanex_dense_mlp(ff), q_temp=(0.2, 128)))
+        layers.append(gamanex_attention_layer(heads, kv, 128, 128, mlp_b, q_temp=(0.2, 128), kv_from=2 * b))
+    return gamanex_config(width, vocab, layers, eps=1e-5, logit_scale=0.5)
