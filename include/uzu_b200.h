@@ -568,12 +568,13 @@ UZU_API void uzu_sigmoid_attention_prepare_encode(uzu_command_buffer* cmd, const
 typedef struct uzu_sigmoid_attention_args {
     uint64_t query, keys, values, out, dynamic_position;
     uint64_t dist_r1, dist_r2, head_bias;   /* optional f32 [heads] */
-    uint64_t partials;             /* scratch f32 [rows, heads, splits, vdim] when splits > 1 */
+    uint64_t partials;             /* scratch f32 [rows, heads, splits, vdim] when splits > 1; tensor-pipe passes with chunk_tiles: f32
+                                      [chunks, rows, heads*vdim], chunks = ceil(ceil((prefix + rows) / 64) / chunk_tiles), 16-byte aligned */
     uint64_t tickets;              /* scratch u32 [rows*heads], zero before the first use (the last split to finish sums the partials in order and zeroes its ticket) */
     uint32_t rows, heads, kv_heads, dim, vdim, prefix, cache_dt;
     float scale;
     uint32_t splits;               /* the causal key range of every query is cut into this many parts, one CTA each (0 / 1 = none) */
-    uint32_t reserved0;
+    uint32_t chunk_tiles;          /* tensor-pipe passes: key tiles (of 64) per CTA, 0 = a CTA walks all keys of its 64 rows */
 } uzu_sigmoid_attention_args;
 UZU_API void uzu_sigmoid_attention_encode(uzu_command_buffer* cmd, const uzu_sigmoid_attention_args* args);
 

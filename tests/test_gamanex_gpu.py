@@ -144,7 +144,7 @@ def test_weighted_gated_combination_of_expert_rows(ctx):
     close(bx.numpy(np.float32, x0.shape), ref.numpy(), 3e-6, "combine")
 
 
-def attention_gpu(ctx, q, k, v, qw, kw, r1, r2, pb, *, heads, kv_heads, dim, vdim, scale, eps, temp, prefix, cache, f32_cache=True, splits=0, own=True):
+def attention_gpu(ctx, q, k, v, qw, kw, r1, r2, pb, *, heads, kv_heads, dim, vdim, scale, eps, temp, prefix, cache, f32_cache=True, splits=0, own=True, chunk_tiles=0):
     """Feeds raw projections [T, ...] of the tokens at positions prefix .. prefix + T - 1 through prepare + attend. `cache` is (keys, values)
     device buffers that persist between calls."""
     T = q.shape[0]
@@ -159,11 +159,11 @@ def attention_gpu(ctx, q, k, v, qw, kw, r1, r2, pb, *, heads, kv_heads, dim, vdi
                                        temp_every=temp[1] if temp else 0, temp_coef=temp[0] if temp else 0.0, epsilon=eps)
     run(ctx, "uzu_sigmoid_attention_prepare_encode", C.byref(pa))
     b1, b2, b3 = ctx.upload(r1.astype(np.float32)), ctx.upload(r2.astype(np.float32)), ctx.upload(pb.astype(np.float32))
-    parts = ctx.upload(np.zeros(max(1, T * heads * max(splits, 1) * vdim), np.float32))
+    parts = ctx.upload(np.zeros(max(1, T * heads * max(splits, 1, (prefix + T + 63) // 64) * vdim), np.float32))
     tickets = ctx.upload(np.zeros(T * heads, np.uint32))
     aa = B.SigmoidAttentionArgs(query=query.ptr, keys=cache[0].ptr, values=cache[1].ptr, out=out.ptr, dist_r1=b1.ptr, dist_r2=b2.ptr, head_bias=b3.ptr,
                                 partials=parts.ptr, tickets=tickets.ptr, rows=T, heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, prefix=prefix,
-                                cache_dt=dt, scale=scale, splits=splits)
+                                cache_dt=dt, scale=scale, splits=splits, chunk_tiles=chunk_tiles)
     run(ctx, "uzu_sigmoid_attention_encode", C.byref(aa))
     assert not tickets.numpy(np.uint32).any(), "every ticket returns to zero"
     return out.numpy(np.float32, (T, heads * vdim)).copy(), query.numpy(np.float32, (T, qn)).copy()
@@ -209,6 +209,11 @@ def test_sigmoid_attention_kernels(ctx, T, prefix, heads, kv_heads, dim, vdim, t
                                    splits=splits, **kw_)
         close(got_q, ref_q, 3e-6, "normed query with temperature")
         close(got, ref, 2e-5 if f32_cache else 2e-4, f"attention, splits {splits}")
+    if not f32_cache and T >= 64:                  # tensor-pipe passes with the key tiles of a row tile cut into chunks
+        for chunk_tiles in (1, 2, 5):
+            got, _ = attention_gpu(ctx, q[prefix:], k[prefix:], v[prefix:], qw, kw, r1, r2, pb, prefix=prefix, cache=cache, f32_cache=False, own=False,
+                                   chunk_tiles=chunk_tiles, **kw_)
+            close(got, ref, 2e-4, f"attention, chunks of {chunk_tiles} key tiles")
 
 
 @pytest.mark.parametrize("far", [0, 1, 31, 32, 33, 500])

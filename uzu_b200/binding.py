@@ -185,7 +185,7 @@ SigmoidAttentionArgs = _struct("uzu_sigmoid_attention_args", [
     ("query", u64), ("keys", u64), ("values", u64), ("out", u64), ("dynamic_position", u64),
     ("dist_r1", u64), ("dist_r2", u64), ("head_bias", u64), ("partials", u64), ("tickets", u64),
     ("rows", u32), ("heads", u32), ("kv_heads", u32), ("dim", u32), ("vdim", u32), ("prefix", u32), ("cache_dt", u32), ("scale", f32),
-    ("splits", u32), ("reserved0", u32)])
+    ("splits", u32), ("chunk_tiles", u32)])
 
 MAIN_SLOT = 0xFFFFFFFF
 

@@ -409,6 +409,7 @@ static void load_gamanex_model(uzu_engine* e, const Json& cfg, const std::string
     e->info.state_bytes_per_token = 0;
 }
 
+constexpr uint32_t kPromptChunks = 8;  // most key chunks of a row tile of a sigmoid-attention prompt pass
 constexpr uint32_t kSplitRows = 256;   // query rows x key splits of one latent-attention launch that leaves partial softmax states
 
 // scratch of the family: f32 row blocks sized by the widest layer
@@ -416,7 +417,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     if (!e->parallel_block) return;
     const uint32_t W = e->model_dim;
     uint32_t proj = 1, lat = 1, wide = 1, query = 1, mixed = 1, gated = 1, gu = 1, act = 1, top = 1, experts = 1, partial = 1, kmax = e->model_dim;
-    uint32_t proj2 = 1, tickets = 1;
+    uint32_t proj2 = 1, tickets = 1, prompt_partial = 0;
     bool second_norm = false;
     for (const Layer& L : e->layers) {
         second_norm = second_norm || L.pre_mlp.present;
@@ -426,6 +427,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
             query = std::max(query, A.heads * A.dim);
             mixed = std::max(mixed, A.heads * A.vdim);
             partial = std::max(partial, A.heads * A.vdim);
+            if (e->store_dt == UZU_DT_BF16) prompt_partial = std::max(prompt_partial, A.heads * A.vdim);    // chunked tensor-pipe prompt passes
             tickets = std::max(tickets, A.heads);
             kmax = std::max(kmax, A.heads * A.vdim);
         } else if (L.kind == MixGeneralDelta) {
@@ -473,7 +475,7 @@ static void create_parallel_block_scratch(uzu_engine* e) {
     P.wide = dev(R * wide * 4);
     P.lat_wide = dev(R * wide * 4);     // unit keys of a prompt pass (generalized delta rule)
     P.query = dev(R * query * 4);
-    P.attn_partial = dev((size_t)kSplitRows * partial * 4);
+    P.attn_partial = dev(std::max((size_t)kSplitRows * partial, (size_t)prompt_partial * kPromptChunks * R) * 4);
     P.mixed = dev(R * mixed * 4);
     P.gated_mix = dev(R * std::max(gated, mixed) * 4);
     P.gate_up = dev(R * top * gu * 4);
@@ -538,14 +540,16 @@ static void encode_sigmoid_attention(uzu_engine* e, uzu_command_buffer* cmd, con
     aa.dist_r1 = A.dist_r1.ptr(); aa.dist_r2 = A.dist_r2.ptr(); aa.head_bias = A.head_bias.ptr();
     aa.rows = m; aa.heads = A.heads; aa.kv_heads = A.kv_heads; aa.dim = A.dim; aa.vdim = A.vdim; aa.prefix = C.length; aa.cache_dt = e->store_dt;
     aa.scale = A.scale;
-    {   // few query rows (decode, short portions): cut the keys so that about two CTAs per SM run (the captured step sizes the cut for the
-        // largest context its graph serves)
+    {   // few query rows (decode, short portions): cut the keys (in tiles of 16) so that about eight small CTAs per SM run and a warp walks
+        // its keys in one to four rounds (the captured step sizes the cut for the largest context its graph serves)
         const uint32_t bound = pc.dynamic ? attention_bucket(C.length + m) : C.length + m;
-        const uint32_t tiles = (bound + 31) / 32;
-        const uint32_t want = std::max(1u, 2u * (uint32_t)e->ctx->sm_count / std::max(1u, m * A.heads));
-        aa.splits = std::min({tiles, want, kSplitRows / std::max(1u, m), 64u});
+        const uint32_t tiles = (bound + 15) / 16;
+        const uint32_t want = std::max(1u, 8u * (uint32_t)e->ctx->sm_count / std::max(1u, m * A.heads));
+        aa.splits = std::min({tiles, want, kSplitRows / std::max(1u, m), 128u});
         aa.partials = P.attn_partial.ptr(); aa.tickets = P.attn_tickets.ptr();
         if (aa.splits < 2 || m > kSplitRows) aa.splits = 1;
+        // long passes on the tensor pipe: at most kPromptChunks chunks of at least 4 key tiles per row tile (the partial tiles fit the scratch)
+        if (!pc.dynamic && m >= 64) aa.chunk_tiles = std::max(4u, ((C.length + m + 63) / 64 + kPromptChunks - 1) / kPromptChunks);
     }
     uzu_sigmoid_attention_encode(cmd, &aa);
     encode_into_residual(e, cmd, A.out, P.mixed.ptr(), A.heads * A.vdim, m, &L.mix_gate, P.proj.ptr(), ld);

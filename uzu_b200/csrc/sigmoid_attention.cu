@@ -4,7 +4,7 @@
 // projection (all heads at once) before they are split into heads. Grouped key / value heads; key and value sizes may differ.
 //   prepare: per token the normed, temperature-scaled query row (f32) and, for a layer that owns its cache, the normed key row and the
 //            value row at the token's position (a layer that reads another layer's cache writes nothing);
-//   attend:  one CTA per (query token, head, split of the keys): a warp per key, lanes across the head's channels (coalesced rows),
+//   attend:  one CTA per (query token, head, split of the keys, in tiles of 16): a warp per key, lanes across the head's channels (coalesced rows),
 //            four keys of a warp in flight; because the weights are not normalised the partial results of the splits simply add: the
 //            last split to finish (a ticket per query and head) adds them in split order, so no second launch and no dependence on
 //            the order of arrival;
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(256) sigmoid_attention_prepare_kernel(const uz
     }
 }
 
-constexpr int SA_WARPS = 4, SA_TILE = 32, SA_UNROLL = 4;
+constexpr int SA_WARPS = 4, SA_TILE = 16, SA_UNROLL = 4;
 
 // WPL = words of a head's key / value row per lane (the larger of the two)
 template <typename T, int EPW, int WPL>
@@ -117,22 +117,36 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sigmoid_attention_kernel(const 
     const T* kbase = reinterpret_cast<const T*>(a.keys) + (size_t)g * a.dim;
     const T* vbase = reinterpret_cast<const T*>(a.values) + (size_t)g * a.vdim;
     const size_t kstride = (size_t)a.kv_heads * a.dim, vstride = (size_t)a.kv_heads * a.vdim;
+    constexpr bool EARLY_V = WPL <= 2;          // small heads: the value words are requested with the key words, before the scores exist
     for (uint32_t j0 = j_begin + warp * SA_UNROLL; j0 < j_end; j0 += SA_WARPS * SA_UNROLL) {
         float s[SA_UNROLL];
+        float vx[EARLY_V ? SA_UNROLL : 1][WPL][EPW];
 #pragma unroll
         for (int u = 0; u < SA_UNROLL; ++u) {
             const uint32_t j = j0 + u;
             s[u] = 0.0f;
             if (j < j_end) {
                 const T* krow = kbase + j * kstride;
+                float kx[WPL][EPW];
+#pragma unroll
+                for (int i = 0; i < WPL; ++i) {
+                    const uint32_t w = lane + 32u * i;
+                    if (w < dwords) sa_load<T, EPW>(krow + (size_t)w * EPW, kx[i]);
+                }
+                if constexpr (EARLY_V) {
+                    const T* vrow = vbase + j * vstride;
+#pragma unroll
+                    for (int i = 0; i < WPL; ++i) {
+                        const uint32_t w = lane + 32u * i;
+                        if (w < vwords) sa_load<T, EPW>(vrow + (size_t)w * EPW, vx[u][i]);
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < WPL; ++i) {
                     const uint32_t w = lane + 32u * i;
                     if (w < dwords) {
-                        float x[EPW];
-                        sa_load<T, EPW>(krow + (size_t)w * EPW, x);
 #pragma unroll
-                        for (int e = 0; e < EPW; ++e) s[u] = fmaf(q[i][e], x[e], s[u]);
+                        for (int e = 0; e < EPW; ++e) s[u] = fmaf(q[i][e], kx[i][e], s[u]);
                     }
                 }
             }
@@ -153,7 +167,12 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sigmoid_attention_kernel(const 
                     const uint32_t w = lane + 32u * i;
                     if (w < vwords) {
                         float x[EPW];
-                        sa_load<T, EPW>(vrow + (size_t)w * EPW, x);
+                        if constexpr (EARLY_V) {
+#pragma unroll
+                            for (int e = 0; e < EPW; ++e) x[e] = vx[u][i][e];
+                        } else {
+                            sa_load<T, EPW>(vrow + (size_t)w * EPW, x);
+                        }
 #pragma unroll
                         for (int e = 0; e < EPW; ++e) acc[i][e] = fmaf(wgt, x[e], acc[i][e]);
                     }
@@ -189,7 +208,15 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sigmoid_attention_kernel(const 
     const float* parts = reinterpret_cast<const float*>(a.partials) + ((size_t)t * a.heads + h) * splits * a.vdim;
     for (uint32_t c = tid; c < a.vdim; c += blockDim.x) {
         float v = 0.0f;
-        for (uint32_t sp = 0; sp < splits; ++sp) v += __ldcg(parts + (size_t)sp * a.vdim + c);
+        uint32_t sp = 0;
+        for (; sp + 8 <= splits; sp += 8) {        // eight loads in flight, added in split order
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = __ldcg(parts + (size_t)(sp + u) * a.vdim + c);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v += x[u];
+        }
+        for (; sp < splits; ++sp) v += __ldcg(parts + (size_t)sp * a.vdim + c);
         out[c] = v;
     }
     if (tid == 0) *ticket = 0;
@@ -261,6 +288,8 @@ void uzu_sigmoid_attention_encode(uzu_command_buffer* cmd, const uzu_sigmoid_att
 //   O += w . V                with w = w_hi + w_lo again, the accumulator fragment of S re-used as the A fragment (two adjacent
 //                             8-key tiles form one 16-key step), V fragments by ldmatrix.trans from the row-major tile.
 // The split keeps the error of the query and of the weights below 2^-16 relative, so only the cache's own bf16 rounding remains.
+// With chunk_tiles the key tiles of a row tile are cut into chunks of that many, one CTA each: late row tiles of a long prompt would
+// otherwise walk many times the keys of early ones while every CTA of the launch is resident from the start.
 namespace uzu {
 
 namespace {
@@ -306,44 +335,49 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const uzu_si
     __nv_bfloat16* k_s = q_lo + SM_BM * ldk;                             // [2][64][ldk]
     __nv_bfloat16* v_s = k_s + 2 * SM_BN * ldk;                          // [2][64][ldv]
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-    const uint32_t m0 = (gridDim.x - 1 - blockIdx.x) * SM_BM, h = blockIdx.y;      // the rows with the most keys start first
-    const uint32_t kvh = h / (a.heads / a.kv_heads);
+    const uint32_t h = blockIdx.y, kvh = h / (a.heads / a.kv_heads);
     const uint32_t prefix = a.dynamic_position ? *reinterpret_cast<const uint32_t*>(a.dynamic_position) : a.prefix;
+    // blockIdx.x counts (row tile, chunk of its key tiles) pairs, the row tiles with the most keys first
+    const uint32_t chunk_tiles = a.chunk_tiles ? a.chunk_tiles : 0xFFFFu;
+    uint32_t mt = (a.rows + SM_BM - 1) / SM_BM, chunk = blockIdx.x, nchunks = 1;
+    while (mt > 0) {
+        --mt;
+        const uint32_t nt = (prefix + min(a.rows, (mt + 1) * SM_BM) + SM_BN - 1) / SM_BN;
+        nchunks = (nt + chunk_tiles - 1) / chunk_tiles;
+        if (chunk < nchunks) break;
+        chunk -= nchunks;
+    }
+    const uint32_t m0 = mt * SM_BM;
     const uint32_t rows_here = min((uint32_t)SM_BM, a.rows - m0);
-    const uint32_t nkeys = prefix + m0 + rows_here, ntiles = (nkeys + SM_BN - 1) / SM_BN;
+    const uint32_t nkeys = prefix + m0 + rows_here, ntiles_all = (nkeys + SM_BN - 1) / SM_BN;
+    const uint32_t t_begin = min(ntiles_all, chunk * chunk_tiles), ntiles = min(ntiles_all, t_begin + chunk_tiles);
+    // scores are kept in units of ln 2: sigmoid(s) = 1 / (1 + 2^(-s log2 e)), and r1 ln(x) log2 e = r1 log2(x)
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float qscale = a.scale * kLog2e;
     const float r1 = a.dist_r1 ? reinterpret_cast<const float*>(a.dist_r1)[h] : 0.0f;
     const float r2 = a.dist_r2 ? reinterpret_cast<const float*>(a.dist_r2)[h] : 0.0f;
-    const float pb = a.head_bias ? reinterpret_cast<const float*>(a.head_bias)[h] : 0.0f;
-    {   // the query tile, scaled, as hi + lo
-        const float* q = reinterpret_cast<const float*>(a.query) + (size_t)m0 * a.heads * dim + (size_t)h * dim;
-        const uint32_t pairs = dim / 2;
-        for (uint32_t i = tid; i < SM_BM * pairs; i += blockDim.x) {
-            const uint32_t r = i / pairs, c = (i - r * pairs) * 2;
-            float2 x = make_float2(0.0f, 0.0f);
-            if (r < rows_here) x = *reinterpret_cast<const float2*>(q + (size_t)r * a.heads * dim + c);
-            uint32_t hi, lo;
-            sm_split_pair(x.x * a.scale, x.y * a.scale, hi, lo);
-            *reinterpret_cast<uint32_t*>(q_hi + r * ldk + c) = hi;
-            *reinterpret_cast<uint32_t*>(q_lo + r * ldk + c) = lo;
-        }
-    }
+    const float pb = (a.head_bias ? reinterpret_cast<const float*>(a.head_bias)[h] : 0.0f) * kLog2e;
     const __nv_bfloat16* keys = reinterpret_cast<const __nv_bfloat16*>(a.keys) + (size_t)kvh * dim;
     const __nv_bfloat16* values = reinterpret_cast<const __nv_bfloat16*>(a.values) + (size_t)kvh * vdim;
     const size_t kstride = (size_t)a.kv_heads * dim, vstride = (size_t)a.kv_heads * vdim;
+    // a thread's 16-byte pieces of a tile: piece tid, tid + 128, ... of rows x (row size / 8); row and column advance without divisions
+    const uint32_t kc = dim / 8, vc = vdim / 8;
+    const uint32_t k_r0 = tid / kc, k_c0 = tid % kc, k_dr = 128 / kc, k_dc = 128 % kc;
+    const uint32_t v_r0 = tid / vc, v_c0 = tid % vc, v_dr = 128 / vc, v_dc = 128 % vc;
+    auto load_rows = [&](__nv_bfloat16* dst_tile, uint32_t ld, const __nv_bfloat16* src, size_t stride, uint32_t j0, uint32_t r, uint32_t c, uint32_t dr,
+                         uint32_t dc, uint32_t pieces_per_row) {
+        while (r < SM_BN) {
+            __nv_bfloat16* dst = dst_tile + r * ld + c * 8;
+            if (j0 + r < nkeys) sm_cp_async16(dst, src + (size_t)(j0 + r) * stride + c * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            r += dr; c += dc;
+            if (c >= pieces_per_row) { c -= pieces_per_row; ++r; }
+        }
+    };
     auto load_tile = [&](uint32_t t, uint32_t buf) {      // rows past the last key are zero: cache pages beyond the context may not exist
-        const uint32_t j0 = t * SM_BN, kc = dim / 8, vc = vdim / 8;
-        for (uint32_t i = tid; i < SM_BN * kc; i += blockDim.x) {
-            const uint32_t r = i / kc, c = (i - r * kc) * 8;
-            __nv_bfloat16* dst = k_s + (buf * SM_BN + r) * ldk + c;
-            if (j0 + r < nkeys) sm_cp_async16(dst, keys + (size_t)(j0 + r) * kstride + c);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
-        for (uint32_t i = tid; i < SM_BN * vc; i += blockDim.x) {
-            const uint32_t r = i / vc, c = (i - r * vc) * 8;
-            __nv_bfloat16* dst = v_s + (buf * SM_BN + r) * ldv + c;
-            if (j0 + r < nkeys) sm_cp_async16(dst, values + (size_t)(j0 + r) * vstride + c);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-        }
+        const uint32_t j0 = t * SM_BN;
+        load_rows(k_s + buf * SM_BN * ldk, ldk, keys, kstride, j0, k_r0, k_c0, k_dr, k_dc, kc);
+        load_rows(v_s + buf * SM_BN * ldv, ldv, values, vstride, j0, v_r0, v_c0, v_dr, v_dc, vc);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     float o[2 * DV][4];
@@ -353,8 +387,31 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const uzu_si
         for (int c = 0; c < 4; ++c) o[n][c] = 0.0f;
     const uint32_t row_lo = warp * 16 + g;                     // this thread's rows of the tile: row_lo and row_lo + 8
     const uint32_t i_lo = prefix + m0 + row_lo, i_warp_last = prefix + m0 + warp * 16 + 15;
-    load_tile(0, 0);
-    for (uint32_t t = 0; t < ntiles; ++t) {
+    load_tile(t_begin, t_begin & 1);
+    {   // the query tile, scaled, as hi + lo; sixteen loads of a thread in flight, behind the first tile's requests
+        const float* q = reinterpret_cast<const float*>(a.query) + (size_t)m0 * a.heads * dim + (size_t)h * dim;
+        const uint32_t pairs = dim / 2, total = SM_BM * pairs;
+        for (uint32_t i0 = tid; i0 < total; i0 += 16 * blockDim.x) {
+            float2 x[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const uint32_t i = i0 + u * blockDim.x, r = i / pairs, c = (i - r * pairs) * 2;
+                x[u] = make_float2(0.0f, 0.0f);
+                if (i < total && r < rows_here) x[u] = *reinterpret_cast<const float2*>(q + (size_t)r * a.heads * dim + c);
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const uint32_t i = i0 + u * blockDim.x, r = i / pairs, c = (i - r * pairs) * 2;
+                if (i < total) {
+                    uint32_t hi, lo;
+                    sm_split_pair(x[u].x * qscale, x[u].y * qscale, hi, lo);
+                    *reinterpret_cast<uint32_t*>(q_hi + r * ldk + c) = hi;
+                    *reinterpret_cast<uint32_t*>(q_lo + r * ldk + c) = lo;
+                }
+            }
+        }
+    }
+    for (uint32_t t = t_begin; t < ntiles; ++t) {
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();                                       // tile t is in place, tile t - 1 is used up
         if (t + 1 < ntiles) load_tile(t + 1, (t + 1) & 1);
@@ -380,26 +437,32 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const uzu_si
                 al[1] = *reinterpret_cast<const uint32_t*>(q_lo + off + 8 * ldk);
                 al[2] = *reinterpret_cast<const uint32_t*>(q_lo + off + 8);
                 al[3] = *reinterpret_cast<const uint32_t*>(q_lo + off + 8 * ldk + 8);
+                uint32_t kb0[8], kb1[8];
 #pragma unroll
                 for (int n = 0; n < 8; ++n) {
                     const __nv_bfloat16* kb = kt + (n * 8 + g) * ldk + kk * 16 + t4 * 2;
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kb), b1 = *reinterpret_cast<const uint32_t*>(kb + 8);
-                    sm_mma(s[n], ah, b0, b1);
-                    sm_mma(s[n], al, b0, b1);
+                    kb0[n] = *reinterpret_cast<const uint32_t*>(kb);
+                    kb1[n] = *reinterpret_cast<const uint32_t*>(kb + 8);
                 }
+                // the hi and the lo product of a tile use the same accumulator: eight other MMAs lie between them
+#pragma unroll
+                for (int n = 0; n < 8; ++n) sm_mma(s[n], ah, kb0[n], kb1[n]);
+#pragma unroll
+                for (int n = 0; n < 8; ++n) sm_mma(s[n], al, kb0[n], kb1[n]);
             }
         }
-        // weights on the fragment: element c of tile n is row row_lo + 8 * (c >> 1), key j0 + n * 8 + t4 * 2 + (c & 1)
+        // weights on the fragment: element c of tile n is row row_lo + 8 * (c >> 1), key j0 + n * 8 + t4 * 2 + (c & 1); its distance
+        // i - j is the thread's base distance plus a constant. Only tiles that reach the diagonal need the mask.
+        const float d0 = (float)((int)i_lo - (int)j0 - (int)(t4 * 2));
+        const bool diagonal = j0 + SM_BN - 1 > prefix + m0 + warp * 16;
 #pragma unroll
         for (int n = 0; n < 8; ++n)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const uint32_t i = i_lo + 8 * (c >> 1), j = j0 + n * 8 + t4 * 2 + (c & 1);
-                float w = 0.0f;
-                if (j <= i) {
-                    const float score = s[n][c] - r1 * __logf(fmaf(r2, (float)(i - j), 1.0f)) + pb;
-                    w = __fdividef(1.0f, 1.0f + __expf(-score));
-                }
+                const float d = d0 + (float)(8 * (c >> 1) - n * 8 - (c & 1));
+                const float score = s[n][c] - r1 * __log2f(fmaf(r2, fmaxf(d, 0.0f), 1.0f)) + pb;
+                float w = __fdividef(1.0f, 1.0f + exp2f(-score));
+                if (diagonal && d < 0.0f) w = 0.0f;
                 s[n][c] = w;
             }
 #pragma unroll
@@ -410,29 +473,69 @@ __global__ void __launch_bounds__(128) sigmoid_attention_mma_kernel(const uzu_si
             sm_split_pair(s[2 * kk + 1][0], s[2 * kk + 1][1], ph[2], pl[2]);
             sm_split_pair(s[2 * kk + 1][2], s[2 * kk + 1][3], ph[3], pl[3]);
 #pragma unroll
-            for (int n = 0; n < DV; ++n) {
+            for (int n = 0; n < DV; n += 2) {      // two 16-column blocks at a time: four independent accumulators between hi and lo
                 if ((uint32_t)n < dv) {
-                    uint32_t b[4];
-                    sm_ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + n * 16 + (lane >> 4) * 8);
+                    const bool two = (uint32_t)n + 1 < dv;
+                    uint32_t b[4], c[4] = {0, 0, 0, 0};
+                    const __nv_bfloat16* vb = vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + (lane >> 4) * 8;
+                    sm_ldmatrix_x4_trans(b, vb + n * 16);
+                    if (two) sm_ldmatrix_x4_trans(c, vb + (n + 1) * 16);
                     sm_mma(o[2 * n], ph, b[0], b[1]);
-                    sm_mma(o[2 * n], pl, b[0], b[1]);
                     sm_mma(o[2 * n + 1], ph, b[2], b[3]);
+                    if (two) {
+                        sm_mma(o[2 * n + 2], ph, c[0], c[1]);
+                        sm_mma(o[2 * n + 3], ph, c[2], c[3]);
+                    }
+                    sm_mma(o[2 * n], pl, b[0], b[1]);
                     sm_mma(o[2 * n + 1], pl, b[2], b[3]);
+                    if (two) {
+                        sm_mma(o[2 * n + 2], pl, c[0], c[1]);
+                        sm_mma(o[2 * n + 3], pl, c[2], c[3]);
+                    }
                 }
             }
         }
     }
-    float* out = reinterpret_cast<float*>(a.out) + (size_t)m0 * a.heads * vdim + (size_t)h * vdim;
+    // one chunk: straight to the output. Several: every chunk leaves its partial tile in `partials` [chunk][row][heads * vdim]; weights are
+    // not normalised, so the partial tiles simply add, and the last chunk to finish adds them in chunk order.
+    const size_t row_stride = (size_t)a.heads * vdim;
+    float* out = reinterpret_cast<float*>(a.out) + (size_t)m0 * row_stride + (size_t)h * vdim;
+    float* mine = nchunks > 1 ? reinterpret_cast<float*>(a.partials) + ((size_t)chunk * a.rows + m0) * row_stride + (size_t)h * vdim : out;
 #pragma unroll
     for (int n = 0; n < 2 * DV; ++n) {
         if ((uint32_t)n < 2 * dv) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 const uint32_t r = row_lo + 8 * half;
-                if (r < rows_here) *reinterpret_cast<float2*>(out + (size_t)r * a.heads * vdim + n * 8 + t4 * 2) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+                if (r < rows_here) *reinterpret_cast<float2*>(mine + (size_t)r * row_stride + n * 8 + t4 * 2) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
             }
         }
     }
+    if (nchunks == 1) return;
+    __shared__ uint32_t is_last;
+    __threadfence();
+    __syncthreads();
+    uint32_t* ticket = reinterpret_cast<uint32_t*>(a.tickets) + (size_t)mt * a.heads + h;
+    if (tid == 0) is_last = atomicAdd(ticket, 1u) == nchunks - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* parts = reinterpret_cast<const float*>(a.partials) + (size_t)m0 * row_stride + (size_t)h * vdim;
+    const uint32_t quads = vdim / 4;
+    for (uint32_t i = tid; i < rows_here * quads; i += blockDim.x) {
+        const uint32_t r = i / quads, c = (i - r * quads) * 4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t c0 = 0; c0 < nchunks; c0 += 4) {          // four chunks' loads in flight, added in chunk order
+            float4 x[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                x[u] = c0 + u < nchunks ? __ldcg(reinterpret_cast<const float4*>(parts + ((size_t)(c0 + u) * a.rows + r) * row_stride + c)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) { v.x += x[u].x; v.y += x[u].y; v.z += x[u].z; v.w += x[u].w; }
+        }
+        *reinterpret_cast<float4*>(out + (size_t)r * row_stride + c) = v;
+    }
+    if (tid == 0) *ticket = 0;
 }
 
 template <int DK, int DV>
@@ -440,7 +543,12 @@ static void launch_sigmoid_attention_mma(uzu_command_buffer* cmd, const uzu_sigm
     const size_t smem = ((size_t)4 * SM_BM * (a.dim + SM_PAD) + (size_t)2 * SM_BN * (a.vdim + SM_PAD)) * sizeof(__nv_bfloat16);
     static std::atomic<uint64_t> opt_in{0};
     opt_in_dynamic_smem(cmd, sigmoid_attention_mma_kernel<DK, DV>, (int)smem, opt_in);
-    launch(cmd, "sigmoid_attention_mma_kernel", sigmoid_attention_mma_kernel<DK, DV>, dim3((a.rows + SM_BM - 1) / SM_BM, a.heads), dim3(128), smem, a);
+    uint32_t ctas = 0;                           // (row tile, chunk) pairs
+    for (uint32_t mt = 0; mt < (a.rows + SM_BM - 1) / SM_BM; ++mt) {
+        const uint32_t nt = (a.prefix + std::min(a.rows, (mt + 1) * SM_BM) + SM_BN - 1) / SM_BN;
+        ctas += a.chunk_tiles ? (nt + a.chunk_tiles - 1) / a.chunk_tiles : 1;
+    }
+    launch(cmd, "sigmoid_attention_mma_kernel", sigmoid_attention_mma_kernel<DK, DV>, dim3(ctas, a.heads), dim3(128), smem, a);
 }
 
 // Shapes the tensor-pipe kernel takes: bf16 caches, passes of >= 64 rows, key and value sizes multiples of 16 up to 128, 16-byte aligned
@@ -448,7 +556,8 @@ static void launch_sigmoid_attention_mma(uzu_command_buffer* cmd, const uzu_sigm
 bool encode_sigmoid_attention_mma(uzu_command_buffer* cmd, const uzu_sigmoid_attention_args& a) {
     static const bool off = getenv("UZU_SIGMOID_NO_MMA") != nullptr;       // A/B runs
     if (off || a.cache_dt != UZU_DT_BF16 || a.rows < SM_BM || a.dim % 16 || a.vdim % 16 || a.dim > 128 || a.vdim > 128) return false;
-    if ((a.keys & 15) || (a.values & 15) || (a.query & 7) || (a.out & 7)) return false;
+    if ((a.keys & 15) || (a.values & 15) || (a.query & 7) || (a.out & 15) || a.dynamic_position) return false;
+    if (a.chunk_tiles && (!a.partials || !a.tickets || (a.partials & 15))) return false;
     const bool k8 = a.dim > 64, v8 = a.vdim > 64;
     if (k8 && v8) launch_sigmoid_attention_mma<8, 8>(cmd, a);
     else if (k8) launch_sigmoid_attention_mma<8, 4>(cmd, a);
