@@ -492,3 +492,46 @@ def test_greedy_generation_through_the_stream(ctx, tmp_path, graph):
     # the stream's state is the context so far: feeding one more token gives the oracle's logits
     pr.check(pr.engine.forward_rows([out[-1]], [0]), ref[-1:], "the stream's state after generation")
     pr.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_runner_command_line(tmp_path, dtype):
+    """bin/trace_run as a user starts it: two requests one after the other, each in portions down to two tokens and single decoded tokens,
+    logits of the wanted places in <step>.f32; the second request reuses the first one's slot."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    cfg = config_a()
+    w = P.random_weights(cfg, 9)
+    model = write_model(tmp_path / "model", cfg, w)
+    reqs = {"a": tokens_for(cfg, 57, 1), "b": tokens_for(cfg, 31, 2)}
+    lines, wanted = [], []
+    step = 0
+    for rid, toks in reqs.items():
+        at, sizes, k = 0, [2, 19, 1, 3, 1, 1, 40], 0
+        while at < len(toks):
+            c = min(sizes[k % len(sizes)], len(toks) - at)
+            want = list(range(c)) if k % 2 == 0 else [c - 1]
+            lines.append(json.dumps({"step": step, "entries": [{"id": rid, "tokens": toks[at:at + c], "want": want}],
+                                     "end": [rid] if at + c == len(toks) else []}))
+            wanted.append((step, rid, [at + x for x in want]))
+            at, k, step = at + c, k + 1, step + 1
+    out = tmp_path / "out"
+    root = Path(__file__).resolve().parents[1]
+    r = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(step)]
+    refs = {rid: P.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    V = cfg["vocab"]
+    errs = []
+    for s, rid, places in wanted:
+        got = np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(len(places), V).astype(np.float64)
+        d = got - refs[rid][places]
+        d = d - d.mean(-1, keepdims=True)
+        errs += list(np.sqrt((d * d).mean(-1)) / refs[rid].std())
+    errs = np.array(errs)
+    if dtype == "float32":
+        assert errs.max() < 2e-4, errs.max()
+    else:
+        assert np.quantile(errs, 0.9) < 6e-2, np.quantile(errs, 0.9)
